@@ -1,0 +1,396 @@
+#!/usr/bin/env python
+"""Benchmark of the L1-attention hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+Prints ONE JSON line.  A step is one forward + one backward of the operator on one batch of
+synthetic, seeded inputs (no dataset exists for this path; the shapes ARE the workload):
+
+  dense_cfg2   q,k ~ N(0,1) fp32 [16,1024,16,64], d_attn ~ N(0,1) [16,1024,1024,16]   (default; the
+               configuration the headline metric is quoted on)
+  dense_cfg3   [2,4096,8,128]
+  sparse_cfg4  bs 8, 4096 tokens, 8 heads, width 64, 131072 edges (self edge + 31 random srcs per dst)
+
+metric: dense  Gop/s          = B*H*T^2*W / (t_fwd + t_bwd), one op = one |q-k| term
+        sparse Gedge-inst/s   = cl*bs*H   / (t_fwd + t_bwd)
+
+value  : device-resident inputs, CUDA-event timed, max over ranks.
+e2e    : the same step through the C ABI's host-buffer entry points (pinned host memory in,
+         host memory out; copies inside the timed region).
+N > 1  : one process per GPU (torchrun); every rank runs the full workload on its own data
+         (weak scaling; the path has no cross-shard reduction, so no data-path collective);
+         value = units of all ranks / slowest rank's time.
+--impl reference : the reference's own CPU implementation (compiled from its sources into
+         oracle/_ref, else the C restatement) on a bounded sample of the same workload.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.join(ROOT, "l1-attention_b200"))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    "dense_cfg2": dict(kind="dense", shape=(16, 1024, 16, 64)),
+    "dense_cfg3": dict(kind="dense", shape=(2, 4096, 8, 128)),
+    "dense_cfg1": dict(kind="dense", shape=(4, 128, 8, 64)),
+    "sparse_cfg4": dict(kind="sparse", shape=(8, 4096, 8, 64), fan=31),
+}
+SM_COUNT, FP32_LANES = 148, 128
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return dict(hbm_gbs=d["hbm_gbs"], sm_max_mhz=d.get("sm_max_mhz", 1965.0), source="measured")
+    return dict(hbm_gbs=6650.0, sm_max_mhz=1965.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.rows, self.proc = [], None
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(index), "--query-gpu=" + self.Q,
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.th = threading.Thread(target=self._read, daemon=True)
+            self.th.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.time(), [x.strip() for x in line.split(",")]))
+
+    def window(self, t0, t1):
+        rows = [r for t, r in self.rows if t0 <= t <= t1] or [r for _, r in self.rows[-3:]]
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": len(rows)}
+        try:
+            sm = sorted(float(r[0]) for r in rows)
+            out["sm_mhz"] = sm[len(sm) // 2]
+            out["sm_max_mhz"] = float(rows[0][1])
+            out["power_w_max"] = max(float(r[2]) for r in rows)
+            names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+            out["reasons"] = [n for i, n in enumerate(names) if any(r[3 + i].lower().startswith("active") for r in rows)]
+        except (IndexError, ValueError):
+            pass
+        return out
+
+    def stop(self):
+        if self.proc:
+            self.proc.terminate()
+
+
+def bench_graph(n, fan, seed):
+    import torch
+    g = torch.Generator().manual_seed(seed)
+    r = torch.rand(n, n, generator=g)
+    r.fill_diagonal_(2)
+    src = r.argsort(1)[:, :fan]
+    rows = torch.cat([torch.stack([torch.arange(n).repeat_interleave(fan), src.reshape(-1)], 1),
+                      torch.stack([torch.arange(n), torch.arange(n)], 1)])
+    return rows[torch.randperm(rows.shape[0], generator=g)]
+
+
+# ----------------------------------------------------------------------------- reference / CPU arm
+
+def cpu_reference_rate(kind, shape, budget_s, fan=31):
+    """Time the reference's CPU implementation on a bounded sample; returns (rate in G units/s, info)."""
+    import numpy as np
+    import torch
+    refdir = os.path.join(ROOT, "oracle", "_ref")
+    have_ref = os.path.exists(os.path.join(refdir, "l1attn_drv_cpp.so"))
+    if have_ref:
+        sys.path.insert(0, refdir)
+        import l1attn_drv_cpp
+        import l1attn_sparse_drv
+        kind_name, dt = "reference", "f64 (the reference CPU extension is float64-only; same seeded values cast up)"
+    else:
+        from oracle import oracle
+        kind_name, dt = "port", "f64"
+    bs, n, h, w = shape
+    gen = torch.Generator().manual_seed(2000)
+
+    def run_dense(t):
+        q = torch.randn(1, t, h, w, generator=gen, dtype=torch.float32).double()
+        k = torch.randn(1, t, h, w, generator=gen, dtype=torch.float32).double()
+        g = torch.randn(1, t, t, h, generator=gen, dtype=torch.float32).double()
+        t0 = time.perf_counter()
+        if have_ref:
+            l1attn_drv_cpp.forward(q, k)
+            l1attn_drv_cpp.backward(g, q, k)
+        else:
+            oracle.dense_fwd(q.numpy(), k.numpy())
+            oracle.dense_bwd(g.numpy(), q.numpy(), k.numpy())
+        return time.perf_counter() - t0, float(h) * t * t * w
+
+    def run_sparse(b):
+        co = bench_graph(n, fan, 4001)
+        from oracle import oracle as orc
+        coo_np, dm, _ = orc.expand_coo(co.numpy())
+        coo = torch.from_numpy(coo_np)
+        q, k, v, dvo = (torch.randn(b, n, h, w, generator=gen, dtype=torch.float32).double() for _ in range(4))
+        t0 = time.perf_counter()
+        if have_ref:
+            vo, attn = l1attn_sparse_drv.forward(v, q, k, coo, dm, True)
+            l1attn_sparse_drv.backward(dvo, v, q, k, coo, attn, dm, True)
+        else:
+            vo, attn = orc.sparse_fwd(v.numpy(), q.numpy(), k.numpy(), coo_np, dm, True)
+            orc.sparse_bwd(dvo.numpy(), v.numpy(), q.numpy(), k.numpy(), coo_np, attn, dm, True)
+        return time.perf_counter() - t0, float(coo.shape[0]) * b * h
+
+    if kind == "dense":
+        run_dense(64)  # warm-up (first call pays page faults / lazy init)
+        t_probe, u_probe = run_dense(128)
+        t = 128
+        while t * 2 <= n and t_probe * ((t * 2) / 128.0) ** 2 <= budget_s:
+            t *= 2
+        el, units = (t_probe, u_probe) if t == 128 else run_dense(t)
+        sample = "one batch item, first %d of %d tokens (B=1,T=%d,H=%d,W=%d), fwd+bwd, %s" % (t, n, t, h, w, dt)
+    else:
+        el, units = run_sparse(1)
+        sample = "one of %d batch items at full graph size (n_tok=%d, %d edges), fwd+bwd, %s" % (bs, n, n * (fan + 1), dt)
+    return units / el / 1e9, dict(kind=kind_name, cores=1, sample=sample, seconds=round(el, 3))
+
+
+def run_reference_arm(args, wl):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    kind, shape = wl["kind"], wl["shape"]
+    per_step = max(1.0, min(20.0, 150.0 / max(1, args.steps + args.warmup)))
+    rates, info = [], None
+    for i in range(args.warmup + args.steps):
+        r, info = cpu_reference_rate(kind, shape, per_step, wl.get("fan", 31))
+        if i >= args.warmup:
+            rates.append(r)
+    val = sum(rates) / len(rates)
+    unit = "Gop/s" if kind == "dense" else "Gedge-inst/s"
+    bs, n, h, w = shape
+    units_full = float(bs) * h * n * n * w if kind == "dense" else float(n * (wl.get("fan", 31) + 1)) * bs * h
+    line = {
+        "impl": "reference", "metric": metric_name(kind), "value": val, "unit": unit, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": units_full / (val * 1e9) * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f64", "data": "synthetic",
+        "config": config_of(args, wl),
+        "cpu_baseline": dict(value=val, unit=unit, cores=info["cores"], kind=info["kind"], sample=info["sample"]),
+        "e2e": {"value": val, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+        "note": "ms_per_step is the full workload extrapolated from the sampled rate",
+    }
+    print(json.dumps(line), flush=True)
+
+
+def metric_name(kind):
+    return "dense L1Attn fwd+bwd Gop/s (B*H*T^2*W)" if kind == "dense" else "sparse COO L1AttnSparse fwd+bwd edge-instances/s"
+
+
+def config_of(args, wl):
+    bs, n, h, w = wl["shape"]
+    c = {"workload": "%s: %s" % (args.workload, "x".join(map(str, wl["shape"]))), "per_gpu_batch": bs,
+         "global_batch": bs * args.gpus, "n_tok": n, "heads": h, "width": w,
+         "partition": "independent batch items per GPU, no collective",
+         "l2": "per-step working set (>= 2 GiB dense, 0.8 GB sparse) exceeds the 126 MB L2; no flush"}
+    if wl["kind"] == "sparse":
+        c["edges"] = n * (wl["fan"] + 1)
+    return c
+
+
+# ----------------------------------------------------------------------------- our arm
+
+def run_ours(args, wl):
+    import torch
+    import torch.distributed as dist
+    import l1attn_cabi as cabi
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device -- this library has no CPU path")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    cabi.lib()
+    kind, shape = wl["kind"], wl["shape"]
+    bs, n, h, w = shape
+    gen = torch.Generator(device=dev).manual_seed(2000 + rank)
+    pk = peaks()
+
+    if kind == "dense":
+        q = torch.randn(shape, generator=gen, device=dev)
+        k = torch.randn(shape, generator=gen, device=dev)
+        g = torch.randn((bs, n, n, h), generator=gen, device=dev)
+        attn = torch.empty((bs, n, n, h), device=dev)
+        dq, dk = torch.empty_like(q), torch.empty_like(k)
+        units = float(bs) * h * n * n * w
+        launches_per_step = 2
+
+        def fwd():
+            cabi.dense_fwd(q, k, out=attn)
+
+        def bwd():
+            cabi.dense_bwd(g, q, k, out=(dq, dk))
+    else:
+        from l1attn_cabi import SparseIndex
+        co = bench_graph(n, wl["fan"], 4001)
+        coo_h, dm, _ = cabi.expand_coo_host(co.numpy())
+        coo = torch.from_numpy(coo_h).to(dev)
+        index = SparseIndex(coo, n, dm)
+        index.check()
+        q, k = (0.25 * torch.randn(shape, generator=gen, device=dev) for _ in range(2))
+        v, dvo = (torch.randn(shape, generator=gen, device=dev) for _ in range(2))
+        vo = torch.empty_like(v)
+        attn = torch.empty((bs, n, dm, h), device=dev)
+        grads = (torch.empty_like(v), None, torch.empty_like(q), torch.empty_like(k))
+        scratch = torch.empty_like(attn)
+        units = float(coo.shape[0]) * bs * h
+        launches_per_step = 4
+
+        def fwd():
+            cabi.sparse_fwd(v, q, k, index, True, out=(vo, attn))
+
+        def bwd():
+            cabi.sparse_bwd(dvo, v, q, k, index, attn, True, out=grads, scratch=scratch)
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        fwd()
+        bwd()
+    sync_all()
+    sampler = ClockSampler(local) if rank == 0 else None
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
+    t_wall0 = time.time()
+    for i in range(args.steps):
+        ev[i][0].record()
+        fwd()
+        ev[i][1].record()
+        bwd()
+        ev[i][2].record()
+    sync_all()
+    t_wall1 = time.time()
+    total_ms = ev[0][0].elapsed_time(ev[-1][2])
+    fwd_ms = sum(e[0].elapsed_time(e[1]) for e in ev) / args.steps
+    bwd_ms = sum(e[1].elapsed_time(e[2]) for e in ev) / args.steps
+    t = torch.tensor([total_ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    total_ms = float(t.item())
+    ms_per_step = total_ms / args.steps
+    value = units * world / (ms_per_step * 1e-3) / 1e9
+    clocks = sampler.window(t_wall0, t_wall1) if sampler else None
+
+    # ---- end to end through the host-buffer C ABI (rank-local; max over ranks)
+    e2e_steps = max(1, min(args.steps, 3))
+    if kind == "dense":
+        hq, hk = (torch.randn(shape).pin_memory() for _ in range(2))
+        hg = torch.randn((bs, n, n, h)).pin_memory()
+        hattn = torch.empty((bs, n, n, h)).pin_memory()
+        hdq, hdk = torch.empty(shape).pin_memory(), torch.empty(shape).pin_memory()
+        nqk, na = hq.numel() * 4, hg.numel() * 4
+        h2d, d2h = 2 * nqk + (na + 2 * nqk), na + 2 * nqk
+
+        def e2e_step():
+            cabi.dense_fwd_host(hq.numpy(), hk.numpy(), out=hattn.numpy())
+            cabi.dense_bwd_host(hg.numpy(), hq.numpy(), hk.numpy(), out=(hdq.numpy(), hdk.numpy()))
+            return float(hdq[0, 0, 0, 0])
+    else:
+        hq, hk, hv, hdvo = (torch.randn(shape).pin_memory() for _ in range(4))
+        coo_np = coo_h
+        nqk, na, nc = hq.numel() * 4, attn.numel() * 4, coo_np.nbytes
+        h2d, d2h = (3 * nqk + nc) + (4 * nqk + na + nc), (nqk + na) + 3 * nqk
+
+        def e2e_step():
+            vo_h, attn_h = cabi.sparse_fwd_host(hv.numpy(), hq.numpy(), hk.numpy(), coo_np, dm, True)
+            r = cabi.sparse_bwd_host(hdvo.numpy(), hv.numpy(), hq.numpy(), hk.numpy(), coo_np, attn_h, dm, True)
+            return float(r[0][0, 0, 0, 0])
+    e2e_step()
+    sync_all()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        e2e_step()
+    torch.cuda.synchronize()
+    e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
+    t = torch.tensor([e2e_ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_ms = float(t.item())
+    e2e_value = units * world / (e2e_ms * 1e-3) / 1e9
+
+    if rank == 0:
+        unit = "Gop/s" if kind == "dense" else "Gedge-inst/s"
+        if kind == "dense":
+            # dominant kernel: the backward.  HBM algorithmic bytes: read d_attn once, read q,k, write d_q,d_k.
+            alg_bytes = 4.0 * (bs * n * n * h + 4 * bs * n * h * w)
+            roof = {"bound": "hbm", "kernel": "dense_bwd_kernel", "achieved": alg_bytes / (bwd_ms * 1e-3) / 1e9,
+                    "peak": pk["hbm_gbs"], "unit": "GB/s", "traffic": None, "peak_source": pk["source"]}
+            roof["frac"] = roof["achieved"] / roof["peak"]
+            mhz = (clocks or {}).get("sm_max_mhz") or pk["sm_max_mhz"]
+            alu_peak = SM_COUNT * FP32_LANES * mhz * 1e6
+            ops = units
+            alu = {"model": "lane-instructions per op: fwd 2 (sub, abs-add), bwd 3 (sub, two adds)",
+                   "peak_lane_instr_per_s": alu_peak, "peak_basis": "148 SM x 128 FP32 lanes x %.0f MHz" % mhz,
+                   "fwd_frac": 2 * ops / (fwd_ms * 1e-3) / alu_peak, "bwd_frac": 3 * ops / (bwd_ms * 1e-3) / alu_peak,
+                   "fwd_bwd_frac": 5 * ops / ((fwd_ms + bwd_ms) * 1e-3) / alu_peak}
+        else:
+            nqk, na, nc = bs * n * h * w * 4.0, attn.numel() * 4.0, coo.numel() * 4.0
+            alg_bytes = (3 * nqk + nqk + na + nc) + (4 * nqk + na + 3 * nqk + nc)
+            roof = {"bound": "hbm", "kernel": "sparse fwd+bwd (4 kernels)", "achieved": alg_bytes / ((fwd_ms + bwd_ms) * 1e-3) / 1e9,
+                    "peak": pk["hbm_gbs"], "unit": "GB/s", "traffic": None, "peak_source": pk["source"]}
+            roof["frac"] = roof["achieved"] / roof["peak"]
+            alu = None
+        cpu = None
+        if world == 1 and not args.no_cpu_baseline:
+            r, info = cpu_reference_rate(kind, shape, 15.0, wl.get("fan", 31))
+            cpu = dict(value=r, unit=unit, cores=info["cores"], kind=info["kind"], sample=info["sample"])
+        line = {
+            "metric": metric_name(kind), "value": value, "unit": unit, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config_of(args, wl),
+            "fwd_ms": fwd_ms, "bwd_ms": bwd_ms, "roofline": roof, "alu_roofline": alu, "cpu_baseline": cpu,
+            "e2e": {"value": e2e_value, "unit": unit, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": e2e_ms, "steps": e2e_steps},
+            "gpu_launches": launches_per_step * args.steps, "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+    if sampler:
+        sampler.stop()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="dense_cfg2", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    wl = WORKLOADS[args.workload]
+    if args.impl == "reference":
+        run_reference_arm(args, wl)
+    else:
+        run_ours(args, wl)
+
+
+if __name__ == "__main__":
+    main()

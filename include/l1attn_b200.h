@@ -1,0 +1,161 @@
+/*
+ * l1attn_b200.h -- C ABI of libl1attn_b200.so: L1-distance attention on NVIDIA B200 (sm_100a).
+ *
+ * Every entry point takes plain pointers and sizes, returns 0 (L1ATTN_OK) or a negative
+ * L1ATTN_ERR_* code, and never calls into Python or PyTorch.  There is no CPU fallback: without a
+ * CUDA device every compute entry point returns L1ATTN_ERR_CUDA.
+ *
+ * Two families:
+ *   *  device-pointer entry points (l1attn_dense_fwd ...): all tensors already live in the
+ *      memory of the CURRENT device; work is enqueued on `stream` (a cudaStream_t passed as
+ *      void*, NULL = the legacy default stream) and the call returns without synchronising.
+ *      They allocate nothing; scratch and index buffers are passed in by the caller.
+ *   *  host-buffer entry points (l1attn_*_host): tensors are in host memory; the call copies
+ *      them to the current device, runs, copies results back and synchronises.  Device memory
+ *      for these calls comes from a grow-only arena per device that the library keeps until
+ *      l1attn_host_release() or process exit.
+ *
+ * Tensor layouts (row-major, contiguous), identical to the reference extension:
+ *   q, k, v, vf, vb, vo and their gradients : [bs][n_tok][n_heads][width]   (v*: v_width)
+ *   dense attn / d_attn                     : [bs][n_tok (key, s)][n_tok (query, t)][n_heads]
+ *   sparse attn                             : [bs][n_tok][dst_mxlen][n_heads]  (post-softmax)
+ *   coo                                     : int32 [cl][4] = {dst, src, dst_rank, src_rank}
+ * dtype: L1ATTN_F32 or L1ATTN_F64 for every floating tensor of a call.
+ *
+ * Reference interfaces these replace are cited per function as file:line of tlh24/l1-attention.
+ */
+#ifndef L1ATTN_B200_H
+#define L1ATTN_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define L1ATTN_OK 0
+#define L1ATTN_ERR_ARG (-1)      /* NULL pointer, negative size, unknown dtype */
+#define L1ATTN_ERR_SHAPE (-2)    /* size beyond what the kernels index (see each function) */
+#define L1ATTN_ERR_CUDA (-3)     /* a CUDA runtime call or launch failed; see l1attn_last_cuda_error() */
+#define L1ATTN_ERR_INDEX (-4)    /* coo holds a token / rank outside [0,n_tok) / [0,dst_mxlen) */
+#define L1ATTN_ERR_NOMEM (-5)    /* host-buffer entry point could not get device memory */
+#define L1ATTN_ERR_ALIGN (-6)    /* a floating tensor pointer is not aligned to its element size */
+
+#define L1ATTN_F32 0
+#define L1ATTN_F64 1
+
+/* Library version (major*10000 + minor*100 + patch). */
+int l1attn_version(void);
+/* Static description of an L1ATTN_ERR_* code. */
+const char *l1attn_strerror(int code);
+/* cudaError_t (as int) of the last failing CUDA call made by this library on this thread, 0 if none. */
+int l1attn_last_cuda_error(void);
+
+/* ------------------------------------------------------------------ dense --------------- */
+
+/*
+ * attn[b][s][t][h] = (-1/sqrt(width)) * sum_w |q[b][t][h][w] - k[b][s][h][w]|.
+ * Replaces l1attn_cuda_drv.forward (cuda/l1attn_cuda_drv.cpp:42-65) and the three launchers
+ * l1attn_cuda_forward{,32,64} (cuda/l1attn_cuda_kernel.cu:457-557).  Any bs, n_tok, n_heads,
+ * width >= 1; every element of attn is written (no memset needed).
+ */
+int l1attn_dense_fwd(const void *q, const void *k, void *attn,
+		     int bs, int n_tok, int n_heads, int width, int dtype, void *stream);
+
+/*
+ * d_q[b][t][h][w] =  scale * sum_s sign(q[b][t][h][w]-k[b][s][h][w]) * d_attn[b][s][t][h]
+ * d_k[b][s][h][w] = -scale * sum_t sign(q[b][t][h][w]-k[b][s][h][w]) * d_attn[b][s][t][h]
+ * with scale = -1/sqrt(width) and sign(0) = 0.  Deterministic (no atomics).
+ * Replaces l1attn_cuda_drv.backward (cuda/l1attn_cuda_drv.cpp:67-104) and
+ * l1attn_cuda_backward{,32,64} (cuda/l1attn_cuda_kernel.cu:559-685).
+ */
+int l1attn_dense_bwd(const void *d_attn, const void *q, const void *k, void *d_q, void *d_k,
+		     int bs, int n_tok, int n_heads, int width, int dtype, void *stream);
+
+/* ------------------------------------------------------------------ sparse -------------- */
+
+/*
+ * Edge index derived from coo, shared by forward and backward of both sparse operators.
+ * l1attn_sparse_index_bytes() gives the size of the device buffer the caller provides;
+ * l1attn_sparse_build_index() fills it (a few small kernels on `stream`).  The index depends
+ * only on (coo, n_tok, dst_mxlen) and can be reused for every call on the same graph.
+ * `status` (device int32, may be NULL) receives 0, or L1ATTN_ERR_INDEX if a row of coo is out
+ * of range; such rows are skipped, never dereferenced.
+ * No counterpart in the reference, whose kernels scatter with atomicAdd per edge
+ * (cuda/l1attn_sparse_cuda_kernel.cu:148-181,327-370) and need no index.
+ */
+size_t l1attn_sparse_index_bytes(int cl, int n_tok, int dst_mxlen);
+int l1attn_sparse_build_index(const int32_t *coo, int cl, int n_tok, int dst_mxlen,
+			      void *index, int32_t *status, void *stream);
+
+/*
+ * Forward of L1AttnSparse (bidi = 0) / L1AttnSparseBidi (bidi = 1):
+ *   x[b][dst][r][h] = scale * sum_w |q[b][dst][h][w] - k[b][src][h][w]|      per coo row (dst,src,r)
+ *   a = exp(x) / (1 + sum_r exp(x))   (use_softmax)   or   a = exp(x)        (slots without an edge: 0)
+ *   vo[b][dst][h][:] += a * v[b][src][h][:]           and, bidi:  vo[b][src][h][:] += a * vb[b][dst][h][:]
+ * Writes every element of vo and attn.  vb is ignored unless bidi.
+ * Replaces l1attn_sparse_cuda_drv.forward (cuda/l1attn_sparse_cuda_drv.cpp:32-46,
+ * cuda/l1attn_sparse_cuda_kernel.cu:373-445) and l1attn_sparse_bidi_cuda_drv.forward
+ * (cuda/l1attn_sparse_bidi_cuda_drv.cpp:34-50, cuda/l1attn_sparse_cuda_kernel.cu:651-725).
+ */
+int l1attn_sparse_fwd(const void *v, const void *vb, const void *q, const void *k,
+		      const void *index, void *vo, void *attn,
+		      int bs, int n_tok, int n_heads, int width, int v_width, int cl, int dst_mxlen,
+		      int use_softmax, int bidi, int dtype, void *stream);
+
+/*
+ * Backward of the same operators.  `attn` is the tensor the forward returned.  `scratch` is a
+ * device buffer of l1attn_sparse_bwd_scratch_bytes() bytes (holds d(logit) per attn slot).
+ * Outputs d_v (d_vf when bidi), d_vb (bidi only, else ignored), d_q, d_k; every element written.
+ * Replaces l1attn_sparse_cuda_drv.backward (cuda/l1attn_sparse_cuda_drv.cpp:48-69,
+ * cuda/l1attn_sparse_cuda_kernel.cu:447-531) and the bidi backward
+ * (cuda/l1attn_sparse_bidi_cuda_drv.cpp:52-75, cuda/l1attn_sparse_cuda_kernel.cu:727-815).
+ */
+size_t l1attn_sparse_bwd_scratch_bytes(int bs, int n_tok, int n_heads, int dst_mxlen, int dtype);
+int l1attn_sparse_bwd(const void *dvo, const void *v, const void *vb, const void *q, const void *k,
+		      const void *index, const void *attn,
+		      void *d_v, void *d_vb, void *d_q, void *d_k, void *scratch,
+		      int bs, int n_tok, int n_heads, int width, int v_width, int cl, int dst_mxlen,
+		      int use_softmax, int bidi, int dtype, void *stream);
+
+/* ------------------------------------------------------------------ expandCoo ----------- */
+
+/*
+ * coo[i] = {dst_i, src_i, #{j<i : dst_j == dst_i}, #{j<i : src_j == src_i}} (int32) from
+ * co = int64 [cl][2] rows {dst, src}; mxlen[0] / mxlen[1] (device int32[2]) receive the largest
+ * dst / src rank + 1 (1 when cl == 0).  Keys must lie in [key_lo, key_lo + n_keys); `counters`
+ * is a device buffer of l1attn_expand_coo_scratch_bytes(n_keys) bytes (may be NULL when that is 0).
+ * Bit-exact replacement of expandCoo (cuda/l1attn_sparse_cuda.py:58-101), which is a Python loop.
+ * l1attn_i64_minmax writes {min, max} over n int64 values to out (device int64[2]).
+ */
+size_t l1attn_expand_coo_scratch_bytes(long long n_keys);
+int l1attn_expand_coo(const int64_t *co, int cl, int32_t *coo, int32_t *mxlen,
+		      long long key_lo, long long n_keys, void *counters, void *stream);
+int l1attn_i64_minmax(const int64_t *x, long long n, int64_t *out, void *stream);
+
+/* ------------------------------------------------------------------ host buffers -------- */
+
+/* Same operations with every tensor in HOST memory (pageable or pinned); synchronous. */
+int l1attn_dense_fwd_host(const void *q, const void *k, void *attn,
+			  int bs, int n_tok, int n_heads, int width, int dtype);
+int l1attn_dense_bwd_host(const void *d_attn, const void *q, const void *k, void *d_q, void *d_k,
+			  int bs, int n_tok, int n_heads, int width, int dtype);
+int l1attn_sparse_fwd_host(const void *v, const void *vb, const void *q, const void *k, const int32_t *coo,
+			   void *vo, void *attn,
+			   int bs, int n_tok, int n_heads, int width, int v_width, int cl, int dst_mxlen,
+			   int use_softmax, int bidi, int dtype);
+int l1attn_sparse_bwd_host(const void *dvo, const void *v, const void *vb, const void *q, const void *k,
+			   const int32_t *coo, const void *attn,
+			   void *d_v, void *d_vb, void *d_q, void *d_k,
+			   int bs, int n_tok, int n_heads, int width, int v_width, int cl, int dst_mxlen,
+			   int use_softmax, int bidi, int dtype);
+/* co int64 [cl][2] -> coo int32 [cl][4]; *dst_mxlen, *src_mxlen as expandCoo returns them. */
+int l1attn_expand_coo_host(const int64_t *co, int cl, int32_t *coo, int *dst_mxlen, int *src_mxlen);
+/* Free the current device's arena used by the *_host entry points. */
+int l1attn_host_release(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* L1ATTN_B200_H */

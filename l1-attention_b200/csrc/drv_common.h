@@ -1,0 +1,44 @@
+// Shared pieces of the three pybind drivers: input checks with the reference's messages
+// (cuda/l1attn_cuda_drv.cpp:38-40), status -> exception, dtype code, current stream.
+#pragma once
+#include <torch/extension.h>
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <vector>
+#include "l1attn_b200.h"
+
+#define CHECK_CUDA(x) TORCH_CHECK(x.device().is_cuda(), #x " must be a CUDA tensor")
+#define CHECK_CONTIGUOUS(x) TORCH_CHECK(x.is_contiguous(), #x " must be contiguous")
+#define CHECK_INPUT(x) \
+	CHECK_CUDA(x);  \
+	CHECK_CONTIGUOUS(x)
+
+inline int l1b_dtype(const torch::Tensor &t, const char *what)
+{
+	if (t.scalar_type() == torch::kFloat32)
+		return L1ATTN_F32;
+	if (t.scalar_type() == torch::kFloat64)
+		return L1ATTN_F64;
+	TORCH_CHECK(false, what, ": expected float32 or float64 tensors, got ", t.scalar_type());
+	return -1;
+}
+
+inline void l1b_same(const torch::Tensor &a, const torch::Tensor &b, const char *an, const char *bn, bool shape = true)
+{
+	TORCH_CHECK(a.scalar_type() == b.scalar_type(), an, " and ", bn, " must have the same dtype");
+	TORCH_CHECK(a.device() == b.device(), an, " and ", bn, " must be on the same device");
+	if (shape)
+		TORCH_CHECK(a.sizes() == b.sizes(), an, " and ", bn, " must have the same shape");
+}
+
+inline void l1b_status(int rc, const char *fn)
+{
+	if (rc == L1ATTN_OK)
+		return;
+	if (rc == L1ATTN_ERR_CUDA || rc == L1ATTN_ERR_NOMEM)
+		TORCH_CHECK(false, fn, ": ", l1attn_strerror(rc), " [",
+			    cudaGetErrorString(static_cast<cudaError_t>(l1attn_last_cuda_error())), "]");
+	TORCH_CHECK(false, fn, ": ", l1attn_strerror(rc));
+}
+
+inline void *l1b_stream() { return static_cast<void *>(at::cuda::getCurrentCUDAStream().stream()); }

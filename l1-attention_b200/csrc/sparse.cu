@@ -1,0 +1,481 @@
+// Sparse (coordinate-list) L1 attention, forward and backward, one- and bi-directional.
+//
+// The reference scatters every edge's contribution with atomicAdd
+// (cuda/l1attn_sparse_cuda_kernel.cu:148-181,183-254,327-370).  Here every output row has one
+// owner: a warp owns a (batch item, token, group of heads) and walks that token's edges, either
+//   * the slots (dst, r) of a destination token    ("dst pass": scores, softmax, vo, d_q, d_vb) or
+//   * the incoming slots of a source token          ("src pass": d_v, d_k, the bidi part of vo),
+// accumulating in registers and storing once.  No atomics, fixed summation order, results are
+// bit-reproducible.  Within a warp LPH lanes share a head and split its width; a head's dot
+// products / L1 sums are finished with xor-shuffles.
+#include <initializer_list>
+#include "common.cuh"
+
+namespace l1b {
+namespace {
+
+struct SparseArgs {
+	int bs, n_tok, n_heads, width, v_width, dm; // dm = dst_mxlen
+	int lph;                                     // lanes per head (power of two <= 32)
+	int use_softmax, bidi;
+	const int32_t *slot_src, *csc_off, *csc_slot;
+};
+
+template <typename T, int VEC> __device__ __forceinline__ Pack<T, VEC> ldv(const T *p, bool ok)
+{
+	Pack<T, VEC> r;
+	if (ok) {
+		r = *reinterpret_cast<const Pack<T, VEC> *>(p);
+	} else {
+#pragma unroll
+		for (int e = 0; e < VEC; e++)
+			r.v[e] = T(0);
+	}
+	return r;
+}
+
+template <typename T> __device__ __forceinline__ T group_sum(T x, int lph)
+{
+	for (int o = lph >> 1; o > 0; o >>= 1)
+		x += __shfl_xor_sync(0xffffffffu, x, o);
+	return x;
+}
+
+// Which (b, tok, head) this lane works on.  Returns false for warps past the end (whole warp).
+struct Who {
+	int b, tok, h, li;
+	bool head_ok;
+};
+__device__ __forceinline__ bool decode(const SparseArgs &a, Who &w)
+{
+	const int lane = threadIdx.x & 31;
+	const int hpw = 32 / a.lph;
+	const int nhc = (a.n_heads + hpw - 1) / hpw;
+	long long gw = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+	const int hc = int(gw % nhc);
+	gw /= nhc;
+	w.tok = int(gw % a.n_tok);
+	const long long b = gw / a.n_tok;
+	if (b >= a.bs)
+		return false;
+	w.b = int(b);
+	w.li = lane % a.lph;
+	w.h = hc * hpw + lane / a.lph;
+	w.head_ok = w.h < a.n_heads;
+	return true;
+}
+
+// ---- forward, dst pass: scores -> exp -> (+1)-softmax -> attn, vo[dst] = sum_r a_r v[src_r] ----
+template <typename T, int VEC>
+__global__ void __launch_bounds__(256) sparse_fwd_dst_kernel(SparseArgs a, const T *__restrict__ v,
+							      const T *__restrict__ q, const T *__restrict__ k,
+							      T *__restrict__ vo, T *attn, T scale)
+{
+	Who w;
+	if (!decode(a, w))
+		return;
+	const int dst = w.tok, H = a.n_heads, W = a.width, Wv = a.v_width, dm = a.dm;
+	const int hh = w.head_ok ? w.h : 0;
+	const size_t tokrow = size_t(w.b) * a.n_tok;
+	const T *qrow = q + ((tokrow + dst) * H + hh) * W;
+	T *arow = attn + ((tokrow + dst) * dm) * H + hh;
+	const int32_t *slots = a.slot_src + size_t(dst) * dm;
+	const int step = a.lph * VEC;
+
+	T denom = T(1);
+	for (int r = 0; r < dm; r++) {
+		const int src = slots[r];
+		T e = T(0);
+		if (src >= 0) {
+			const T *krow = k + ((tokrow + src) * H + hh) * W;
+			T part = T(0);
+			for (int x = w.li * VEC; x < W; x += step) {
+				const Pack<T, VEC> qv = ldv<T, VEC>(qrow + x, w.head_ok);
+				const Pack<T, VEC> kv = ldv<T, VEC>(krow + x, w.head_ok);
+#pragma unroll
+				for (int i = 0; i < VEC; i++)
+					part += absdiff(qv.v[i], kv.v[i]);
+			}
+			part = group_sum(part, a.lph);
+			e = exp_t(part * scale);
+			denom += e;
+		}
+		if (w.li == 0 && w.head_ok)
+			arow[size_t(r) * H] = e;
+	}
+	__syncwarp();
+	if (a.use_softmax && w.head_ok)
+		for (int r = w.li; r < dm; r += a.lph)
+			arow[size_t(r) * H] = arow[size_t(r) * H] / denom;
+	__syncwarp();
+
+	T *orow = vo + ((tokrow + dst) * H + hh) * Wv;
+	for (int x = w.li * VEC; x < Wv; x += step) {
+		Pack<T, VEC> acc = ldv<T, VEC>(nullptr, false);
+		for (int r = 0; r < dm; r++) {
+			const int src = slots[r];
+			if (src < 0)
+				continue;
+			const T ar = w.head_ok ? arow[size_t(r) * H] : T(0);
+			const Pack<T, VEC> vv = ldv<T, VEC>(v + ((tokrow + src) * H + hh) * Wv + x, w.head_ok);
+#pragma unroll
+			for (int i = 0; i < VEC; i++)
+				acc.v[i] += ar * vv.v[i];
+		}
+		if (w.head_ok)
+			*reinterpret_cast<Pack<T, VEC> *>(orow + x) = acc;
+	}
+}
+
+// ---- forward, src pass (bidi only): vo[src] += sum_{incoming (dst,r)} a[dst][r] * vb[dst] ----
+template <typename T, int VEC>
+__global__ void __launch_bounds__(256) sparse_fwd_src_kernel(SparseArgs a, const T *__restrict__ vb,
+							      const T *__restrict__ attn, T *vo)
+{
+	Who w;
+	if (!decode(a, w))
+		return;
+	if (!w.head_ok)
+		return;
+	const int src = w.tok, H = a.n_heads, Wv = a.v_width, dm = a.dm;
+	const size_t tokrow = size_t(w.b) * a.n_tok;
+	const int e0 = a.csc_off[src], e1 = a.csc_off[src + 1];
+	const int step = a.lph * VEC;
+	T *orow = vo + ((tokrow + src) * H + w.h) * Wv;
+	for (int x = w.li * VEC; x < Wv; x += step) {
+		Pack<T, VEC> acc = ldv<T, VEC>(nullptr, false);
+		for (int e = e0; e < e1; e++) {
+			const int slot = a.csc_slot[e];
+			const int dst = slot / dm;
+			const T ar = attn[(tokrow * dm + slot) * H + w.h];
+			const Pack<T, VEC> vv = ldv<T, VEC>(vb + ((tokrow + dst) * H + w.h) * Wv + x, true);
+#pragma unroll
+			for (int i = 0; i < VEC; i++)
+				acc.v[i] += ar * vv.v[i];
+		}
+		Pack<T, VEC> cur = ldv<T, VEC>(orow + x, true);
+#pragma unroll
+		for (int i = 0; i < VEC; i++)
+			cur.v[i] += acc.v[i];
+		*reinterpret_cast<Pack<T, VEC> *>(orow + x) = cur;
+	}
+}
+
+// ---- backward, dst pass: ds_r, softmax Jacobian in closed form, dx_r -> scratch, d_q, (d_vb) ----
+//   ds_r = <v[src_r], dvo[dst]>  (+ <vb[dst], dvo[src_r]> when bidi)
+//   softmax: dx_r = a_r (ds_r - sum_j a_j ds_j)   [same as the reference's Jacobian product,
+//            cuda/l1attn_sparse_cuda_kernel.cu:256-295, without its O(dst_mxlen^2) loop]
+//   else:    dx_r = a_r ds_r
+template <typename T, int VEC>
+__global__ void __launch_bounds__(256) sparse_bwd_dst_kernel(SparseArgs a, const T *__restrict__ dvo,
+							      const T *__restrict__ v, const T *__restrict__ vb,
+							      const T *__restrict__ q, const T *__restrict__ k,
+							      const T *__restrict__ attn, T *dx, T *__restrict__ d_q,
+							      T *__restrict__ d_vb, T scale)
+{
+	Who w;
+	if (!decode(a, w))
+		return;
+	const int dst = w.tok, H = a.n_heads, W = a.width, Wv = a.v_width, dm = a.dm;
+	const int hh = w.head_ok ? w.h : 0;
+	const size_t tokrow = size_t(w.b) * a.n_tok;
+	const size_t aoff = ((tokrow + dst) * dm) * H + hh;
+	const T *arow = attn + aoff;
+	T *xrow = dx + aoff;
+	const int32_t *slots = a.slot_src + size_t(dst) * dm;
+	const int step = a.lph * VEC;
+	const T *gdst = dvo + ((tokrow + dst) * H + hh) * Wv;
+
+	T S = T(0);
+	for (int r = 0; r < dm; r++) {
+		const int src = slots[r];
+		if (src < 0)
+			continue;
+		T part = T(0);
+		for (int x = w.li * VEC; x < Wv; x += step) {
+			const Pack<T, VEC> vv = ldv<T, VEC>(v + ((tokrow + src) * H + hh) * Wv + x, w.head_ok);
+			const Pack<T, VEC> gv = ldv<T, VEC>(gdst + x, w.head_ok);
+#pragma unroll
+			for (int i = 0; i < VEC; i++)
+				part += vv.v[i] * gv.v[i];
+			if (a.bidi) {
+				const Pack<T, VEC> bv = ldv<T, VEC>(vb + ((tokrow + dst) * H + hh) * Wv + x, w.head_ok);
+				const Pack<T, VEC> gs = ldv<T, VEC>(dvo + ((tokrow + src) * H + hh) * Wv + x, w.head_ok);
+#pragma unroll
+				for (int i = 0; i < VEC; i++)
+					part += bv.v[i] * gs.v[i];
+			}
+		}
+		const T ds = group_sum(part, a.lph);
+		const T ar = w.head_ok ? arow[size_t(r) * H] : T(0);
+		S += ar * ds;
+		if (w.li == 0 && w.head_ok)
+			xrow[size_t(r) * H] = ds;
+	}
+	__syncwarp();
+	if (w.head_ok)
+		for (int r = w.li; r < dm; r += a.lph) {
+			if (slots[r] < 0)
+				continue;
+			const T ar = arow[size_t(r) * H], ds = xrow[size_t(r) * H];
+			xrow[size_t(r) * H] = a.use_softmax ? ar * (ds - S) : ar * ds;
+		}
+	__syncwarp();
+
+	const T *qrow = q + ((tokrow + dst) * H + hh) * W;
+	T *orow = d_q + ((tokrow + dst) * H + hh) * W;
+	for (int x = w.li * VEC; x < W; x += step) {
+		const Pack<T, VEC> qv = ldv<T, VEC>(qrow + x, w.head_ok);
+		Pack<T, VEC> acc = ldv<T, VEC>(nullptr, false);
+		for (int r = 0; r < dm; r++) {
+			const int src = slots[r];
+			if (src < 0)
+				continue;
+			const T dxr = w.head_ok ? xrow[size_t(r) * H] : T(0);
+			const Pack<T, VEC> kv = ldv<T, VEC>(k + ((tokrow + src) * H + hh) * W + x, w.head_ok);
+#pragma unroll
+			for (int i = 0; i < VEC; i++)
+				acc.v[i] += sign_apply(qv.v[i] - kv.v[i], dxr);
+		}
+		if (w.head_ok) {
+#pragma unroll
+			for (int i = 0; i < VEC; i++)
+				acc.v[i] *= scale;
+			*reinterpret_cast<Pack<T, VEC> *>(orow + x) = acc;
+		}
+	}
+	if (a.bidi) { // d_vb[dst] = sum_r a_r dvo[src_r]
+		T *brow = d_vb + ((tokrow + dst) * H + hh) * Wv;
+		for (int x = w.li * VEC; x < Wv; x += step) {
+			Pack<T, VEC> acc = ldv<T, VEC>(nullptr, false);
+			for (int r = 0; r < dm; r++) {
+				const int src = slots[r];
+				if (src < 0)
+					continue;
+				const T ar = w.head_ok ? arow[size_t(r) * H] : T(0);
+				const Pack<T, VEC> gs = ldv<T, VEC>(dvo + ((tokrow + src) * H + hh) * Wv + x, w.head_ok);
+#pragma unroll
+				for (int i = 0; i < VEC; i++)
+					acc.v[i] += ar * gs.v[i];
+			}
+			if (w.head_ok)
+				*reinterpret_cast<Pack<T, VEC> *>(brow + x) = acc;
+		}
+	}
+}
+
+// ---- backward, src pass: d_v[src] = sum a dvo[dst];  d_k[src] = -scale sum sign(q[dst]-k[src]) dx ----
+template <typename T, int VEC>
+__global__ void __launch_bounds__(256) sparse_bwd_src_kernel(SparseArgs a, const T *__restrict__ dvo,
+							      const T *__restrict__ q, const T *__restrict__ k,
+							      const T *__restrict__ attn, const T *__restrict__ dx,
+							      T *__restrict__ d_v, T *__restrict__ d_k, T scale)
+{
+	Who w;
+	if (!decode(a, w))
+		return;
+	if (!w.head_ok)
+		return;
+	const int src = w.tok, H = a.n_heads, W = a.width, Wv = a.v_width, dm = a.dm;
+	const size_t tokrow = size_t(w.b) * a.n_tok;
+	const int e0 = a.csc_off[src], e1 = a.csc_off[src + 1];
+	const int step = a.lph * VEC;
+	T *vrow = d_v + ((tokrow + src) * H + w.h) * Wv;
+	for (int x = w.li * VEC; x < Wv; x += step) {
+		Pack<T, VEC> acc = ldv<T, VEC>(nullptr, false);
+		for (int e = e0; e < e1; e++) {
+			const int slot = a.csc_slot[e];
+			const int dst = slot / dm;
+			const T ar = attn[(tokrow * dm + slot) * H + w.h];
+			const Pack<T, VEC> gv = ldv<T, VEC>(dvo + ((tokrow + dst) * H + w.h) * Wv + x, true);
+#pragma unroll
+			for (int i = 0; i < VEC; i++)
+				acc.v[i] += ar * gv.v[i];
+		}
+		*reinterpret_cast<Pack<T, VEC> *>(vrow + x) = acc;
+	}
+	const T *krow = k + ((tokrow + src) * H + w.h) * W;
+	T *orow = d_k + ((tokrow + src) * H + w.h) * W;
+	for (int x = w.li * VEC; x < W; x += step) {
+		const Pack<T, VEC> kv = ldv<T, VEC>(krow + x, true);
+		Pack<T, VEC> acc = ldv<T, VEC>(nullptr, false);
+		for (int e = e0; e < e1; e++) {
+			const int slot = a.csc_slot[e];
+			const int dst = slot / dm;
+			const T dxr = dx[(tokrow * dm + slot) * H + w.h];
+			const Pack<T, VEC> qv = ldv<T, VEC>(q + ((tokrow + dst) * H + w.h) * W + x, true);
+#pragma unroll
+			for (int i = 0; i < VEC; i++)
+				acc.v[i] += sign_apply(qv.v[i] - kv.v[i], dxr);
+		}
+#pragma unroll
+		for (int i = 0; i < VEC; i++)
+			acc.v[i] *= -scale;
+		*reinterpret_cast<Pack<T, VEC> *>(orow + x) = acc;
+	}
+}
+
+int pow2_ceil(int x)
+{
+	int p = 1;
+	while (p < x)
+		p <<= 1;
+	return p;
+}
+
+struct Grid {
+	unsigned blocks;
+	bool ok;
+};
+Grid grid_for(const SparseArgs &a)
+{
+	const int hpw = 32 / a.lph;
+	const long long warps = (long long)a.bs * a.n_tok * ((a.n_heads + hpw - 1) / hpw);
+	const long long blocks = (warps + 7) / 8;
+	return {unsigned(blocks), blocks <= 0x7fffffffLL};
+}
+
+template <typename T, int VEC>
+int fwd_t(SparseArgs a, const T *v, const T *vb, const T *q, const T *k, T *vo, T *attn, cudaStream_t st)
+{
+	const int mw = a.width > a.v_width ? a.width : a.v_width;
+	a.lph = pow2_ceil((mw + VEC - 1) / VEC);
+	if (a.lph > 32)
+		a.lph = 32;
+	const Grid g = grid_for(a);
+	if (!g.ok)
+		return L1ATTN_ERR_SHAPE;
+	const T scale = T(-1.0 / sqrt(double(a.width)));
+	sparse_fwd_dst_kernel<T, VEC><<<g.blocks, 256, 0, st>>>(a, v, q, k, vo, attn, scale);
+	L1B_LAUNCH_CHECK();
+	if (a.bidi) {
+		sparse_fwd_src_kernel<T, VEC><<<g.blocks, 256, 0, st>>>(a, vb, attn, vo);
+		L1B_LAUNCH_CHECK();
+	}
+	return L1ATTN_OK;
+}
+
+template <typename T, int VEC>
+int bwd_t(SparseArgs a, const T *dvo, const T *v, const T *vb, const T *q, const T *k, const T *attn, T *d_v,
+	  T *d_vb, T *d_q, T *d_k, T *dx, cudaStream_t st)
+{
+	const int mw = a.width > a.v_width ? a.width : a.v_width;
+	a.lph = pow2_ceil((mw + VEC - 1) / VEC);
+	if (a.lph > 32)
+		a.lph = 32;
+	const Grid g = grid_for(a);
+	if (!g.ok)
+		return L1ATTN_ERR_SHAPE;
+	const T scale = T(-1.0 / sqrt(double(a.width)));
+	sparse_bwd_dst_kernel<T, VEC><<<g.blocks, 256, 0, st>>>(a, dvo, v, vb, q, k, attn, dx, d_q, d_vb, scale);
+	L1B_LAUNCH_CHECK();
+	sparse_bwd_src_kernel<T, VEC><<<g.blocks, 256, 0, st>>>(a, dvo, q, k, attn, dx, d_v, d_k, scale);
+	L1B_LAUNCH_CHECK();
+	return L1ATTN_OK;
+}
+
+bool all_aligned16(std::initializer_list<const void *> ps)
+{
+	for (const void *p : ps)
+		if (p && !aligned(p, 16))
+			return false;
+	return true;
+}
+
+} // namespace
+} // namespace l1b
+
+using namespace l1b;
+
+extern "C" size_t l1attn_sparse_bwd_scratch_bytes(int bs, int n_tok, int n_heads, int dst_mxlen, int dtype)
+{
+	if (bs < 0 || n_tok < 0 || n_heads < 0 || dst_mxlen < 0)
+		return 0;
+	const size_t n = size_t(bs) * n_tok * dst_mxlen * n_heads * (dtype == L1ATTN_F64 ? 8 : 4);
+	return n ? n : 16;
+}
+
+static int check_sparse(int bs, int n_tok, int n_heads, int width, int v_width, int cl, int dst_mxlen, int dtype)
+{
+	if (bs < 0 || n_tok < 0 || n_heads < 0 || width < 1 || v_width < 1 || cl < 0 || dst_mxlen < 0)
+		return L1ATTN_ERR_ARG;
+	if (dtype != L1ATTN_F32 && dtype != L1ATTN_F64)
+		return L1ATTN_ERR_ARG;
+	if ((long long)n_tok * dst_mxlen > 0x7fffffffLL)
+		return L1ATTN_ERR_SHAPE;
+	return L1ATTN_OK;
+}
+
+extern "C" int l1attn_sparse_fwd(const void *v, const void *vb, const void *q, const void *k, const void *index,
+				  void *vo, void *attn, int bs, int n_tok, int n_heads, int width, int v_width, int cl,
+				  int dst_mxlen, int use_softmax, int bidi, int dtype, void *stream)
+{
+	int rc = check_sparse(bs, n_tok, n_heads, width, v_width, cl, dst_mxlen, dtype);
+	if (rc)
+		return rc;
+	if (bs == 0 || n_tok == 0 || n_heads == 0)
+		return L1ATTN_OK;
+	if (!v || !q || !k || !index || !vo || !attn || (bidi && !vb))
+		return L1ATTN_ERR_ARG;
+	const size_t es = dtype == L1ATTN_F64 ? 8 : 4;
+	for (const void *p : {v, vb, q, k, (const void *)vo, (const void *)attn})
+		if (p && !aligned(p, es))
+			return L1ATTN_ERR_ALIGN;
+	cudaStream_t st = static_cast<cudaStream_t>(stream);
+	SparseIndex ix = sparse_index_view(const_cast<void *>(index), cl, n_tok, dst_mxlen);
+	SparseArgs a{bs, n_tok, n_heads, width, v_width, dst_mxlen, 32, use_softmax != 0, bidi != 0,
+		     ix.slot_src, ix.csc_off, ix.csc_slot};
+	const bool a16 = all_aligned16({v, vb, q, k, vo});
+	if (dtype == L1ATTN_F32) {
+		if (a16 && width % 4 == 0 && v_width % 4 == 0)
+			return fwd_t<float, 4>(a, (const float *)v, (const float *)vb, (const float *)q, (const float *)k,
+					       (float *)vo, (float *)attn, st);
+		return fwd_t<float, 1>(a, (const float *)v, (const float *)vb, (const float *)q, (const float *)k,
+				       (float *)vo, (float *)attn, st);
+	}
+	if (a16 && width % 2 == 0 && v_width % 2 == 0)
+		return fwd_t<double, 2>(a, (const double *)v, (const double *)vb, (const double *)q, (const double *)k,
+					(double *)vo, (double *)attn, st);
+	return fwd_t<double, 1>(a, (const double *)v, (const double *)vb, (const double *)q, (const double *)k,
+				(double *)vo, (double *)attn, st);
+}
+
+extern "C" int l1attn_sparse_bwd(const void *dvo, const void *v, const void *vb, const void *q, const void *k,
+				  const void *index, const void *attn, void *d_v, void *d_vb, void *d_q, void *d_k,
+				  void *scratch, int bs, int n_tok, int n_heads, int width, int v_width, int cl,
+				  int dst_mxlen, int use_softmax, int bidi, int dtype, void *stream)
+{
+	int rc = check_sparse(bs, n_tok, n_heads, width, v_width, cl, dst_mxlen, dtype);
+	if (rc)
+		return rc;
+	if (bs == 0 || n_tok == 0 || n_heads == 0)
+		return L1ATTN_OK;
+	if (!dvo || !v || !q || !k || !index || !attn || !d_v || !d_q || !d_k || !scratch || (bidi && (!vb || !d_vb)))
+		return L1ATTN_ERR_ARG;
+	const size_t es = dtype == L1ATTN_F64 ? 8 : 4;
+	for (const void *p : {dvo, v, vb, q, k, attn, (const void *)d_v, (const void *)d_vb, (const void *)d_q,
+			      (const void *)d_k, (const void *)scratch})
+		if (p && !aligned(p, es))
+			return L1ATTN_ERR_ALIGN;
+	cudaStream_t st = static_cast<cudaStream_t>(stream);
+	SparseIndex ix = sparse_index_view(const_cast<void *>(index), cl, n_tok, dst_mxlen);
+	SparseArgs a{bs, n_tok, n_heads, width, v_width, dst_mxlen, 32, use_softmax != 0, bidi != 0,
+		     ix.slot_src, ix.csc_off, ix.csc_slot};
+	const bool a16 = all_aligned16({dvo, v, vb, q, k, d_v, d_vb, d_q, d_k});
+	if (dtype == L1ATTN_F32) {
+		if (a16 && width % 4 == 0 && v_width % 4 == 0)
+			return bwd_t<float, 4>(a, (const float *)dvo, (const float *)v, (const float *)vb, (const float *)q,
+					       (const float *)k, (const float *)attn, (float *)d_v, (float *)d_vb,
+					       (float *)d_q, (float *)d_k, (float *)scratch, st);
+		return bwd_t<float, 1>(a, (const float *)dvo, (const float *)v, (const float *)vb, (const float *)q,
+				       (const float *)k, (const float *)attn, (float *)d_v, (float *)d_vb, (float *)d_q,
+				       (float *)d_k, (float *)scratch, st);
+	}
+	if (a16 && width % 2 == 0 && v_width % 2 == 0)
+		return bwd_t<double, 2>(a, (const double *)dvo, (const double *)v, (const double *)vb, (const double *)q,
+					(const double *)k, (const double *)attn, (double *)d_v, (double *)d_vb,
+					(double *)d_q, (double *)d_k, (double *)scratch, st);
+	return bwd_t<double, 1>(a, (const double *)dvo, (const double *)v, (const double *)vb, (const double *)q,
+				(const double *)k, (const double *)attn, (double *)d_v, (double *)d_vb, (double *)d_q,
+				(double *)d_k, (double *)scratch, st);
+}

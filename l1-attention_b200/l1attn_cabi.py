@@ -1,0 +1,241 @@
+"""ctypes binding of libl1attn_b200.so (the C ABI declared in include/l1attn_b200.h).
+
+Two layers:
+  * `lib()` -- the loaded library with argument types set; raises if it has not been built.
+  * thin helpers that take numpy arrays in HOST memory (the *_host entry points: copies in,
+    runs on the current CUDA device, copies out) or torch CUDA tensors (device-pointer entry
+    points, enqueued on the current torch stream, no synchronisation).
+
+Nothing here computes on the CPU: without the library or without a GPU the calls fail.
+"""
+import ctypes
+import os
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libl1attn_b200.so")
+F32, F64 = 0, 1
+
+_c = ctypes
+_vp, _i, _ll, _sz = _c.c_void_p, _c.c_int, _c.c_longlong, _c.c_size_t
+# name -> (restype, argtypes); one entry per declaration in include/l1attn_b200.h
+SIGNATURES = {
+    "l1attn_version": (_i, []),
+    "l1attn_strerror": (_c.c_char_p, [_i]),
+    "l1attn_last_cuda_error": (_i, []),
+    "l1attn_dense_fwd": (_i, [_vp] * 3 + [_i] * 5 + [_vp]),
+    "l1attn_dense_bwd": (_i, [_vp] * 5 + [_i] * 5 + [_vp]),
+    "l1attn_sparse_index_bytes": (_sz, [_i] * 3),
+    "l1attn_sparse_build_index": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp]),
+    "l1attn_sparse_fwd": (_i, [_vp] * 7 + [_i] * 10 + [_vp]),
+    "l1attn_sparse_bwd_scratch_bytes": (_sz, [_i] * 5),
+    "l1attn_sparse_bwd": (_i, [_vp] * 12 + [_i] * 10 + [_vp]),
+    "l1attn_expand_coo_scratch_bytes": (_sz, [_ll]),
+    "l1attn_expand_coo": (_i, [_vp, _i, _vp, _vp, _ll, _ll, _vp, _vp]),
+    "l1attn_i64_minmax": (_i, [_vp, _ll, _vp, _vp]),
+    "l1attn_dense_fwd_host": (_i, [_vp] * 3 + [_i] * 5),
+    "l1attn_dense_bwd_host": (_i, [_vp] * 5 + [_i] * 5),
+    "l1attn_sparse_fwd_host": (_i, [_vp] * 7 + [_i] * 10),
+    "l1attn_sparse_bwd_host": (_i, [_vp] * 11 + [_i] * 10),
+    "l1attn_expand_coo_host": (_i, [_vp, _i, _vp, _c.POINTER(_i), _c.POINTER(_i)]),
+    "l1attn_host_release": (_i, []),
+}
+
+_LIB = None
+
+
+class L1AttnError(RuntimeError):
+    def __init__(self, code, where):
+        self.code = code
+        msg = lib().l1attn_strerror(code).decode()
+        super().__init__("%s: %s (code %d, cuda error %d)" % (where, msg, code, lib().l1attn_last_cuda_error()))
+
+
+def lib():
+    """Load libl1attn_b200.so.  There is no fallback: a missing library is an error."""
+    global _LIB
+    if _LIB is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError("%s not built -- run `python build.py` in %s" % (LIB_PATH, _HERE))
+        l = ctypes.CDLL(LIB_PATH, mode=ctypes.RTLD_GLOBAL)
+        for name, (res, args) in SIGNATURES.items():
+            f = getattr(l, name)
+            f.restype, f.argtypes = res, args
+        _LIB = l
+    return _LIB
+
+
+def _check(rc, where):
+    if rc != 0:
+        raise L1AttnError(rc, where)
+
+
+# ------------------------------------------------------------------ host (numpy) helpers
+
+def _np(a, dtype=None):
+    return np.ascontiguousarray(a, dtype=dtype)
+
+
+def _dt(a):
+    if a.dtype == np.float32:
+        return F32
+    if a.dtype == np.float64:
+        return F64
+    raise TypeError("float32 or float64 expected, got %s" % a.dtype)
+
+
+def _ptr(a):
+    return None if a is None else a.ctypes.data
+
+
+def dense_fwd_host(q, k, out=None):
+    q = _np(q)
+    k = _np(k, q.dtype)
+    bs, n, h, w = q.shape
+    attn = np.empty((bs, n, n, h), dtype=q.dtype) if out is None else out
+    _check(lib().l1attn_dense_fwd_host(_ptr(q), _ptr(k), _ptr(attn), bs, n, h, w, _dt(q)), "l1attn_dense_fwd_host")
+    return attn
+
+
+def dense_bwd_host(d_attn, q, k, out=None):
+    q = _np(q)
+    k, d_attn = _np(k, q.dtype), _np(d_attn, q.dtype)
+    bs, n, h, w = q.shape
+    dq, dk = (np.empty_like(q), np.empty_like(q)) if out is None else out
+    _check(lib().l1attn_dense_bwd_host(_ptr(d_attn), _ptr(q), _ptr(k), _ptr(dq), _ptr(dk), bs, n, h, w, _dt(q)),
+           "l1attn_dense_bwd_host")
+    return dq, dk
+
+
+def sparse_fwd_host(v, q, k, coo, dst_mxlen, use_softmax=True, vb=None):
+    """vb given -> bidirectional operator.  Returns (vo, attn)."""
+    q = _np(q)
+    k, v = _np(k, q.dtype), _np(v, q.dtype)
+    vb = None if vb is None else _np(vb, q.dtype)
+    coo = _np(coo, np.int32)
+    bs, n, h, w = q.shape
+    wv = v.shape[3]
+    vo = np.empty((bs, n, h, wv), dtype=q.dtype)
+    attn = np.empty((bs, n, int(dst_mxlen), h), dtype=q.dtype)
+    _check(lib().l1attn_sparse_fwd_host(_ptr(v), _ptr(vb), _ptr(q), _ptr(k), _ptr(coo), _ptr(vo), _ptr(attn),
+                                        bs, n, h, w, wv, coo.shape[0], int(dst_mxlen), int(bool(use_softmax)),
+                                        int(vb is not None), _dt(q)), "l1attn_sparse_fwd_host")
+    return vo, attn
+
+
+def sparse_bwd_host(dvo, v, q, k, coo, attn, dst_mxlen, use_softmax=True, vb=None):
+    """Returns (d_v, d_q, d_k) or, with vb, (d_vf, d_vb, d_q, d_k)."""
+    q = _np(q)
+    k, v, dvo, attn = _np(k, q.dtype), _np(v, q.dtype), _np(dvo, q.dtype), _np(attn, q.dtype)
+    vb = None if vb is None else _np(vb, q.dtype)
+    coo = _np(coo, np.int32)
+    bs, n, h, w = q.shape
+    wv = v.shape[3]
+    dv, dq, dk = np.empty_like(v), np.empty_like(q), np.empty_like(q)
+    dvb = np.empty_like(v) if vb is not None else None
+    _check(lib().l1attn_sparse_bwd_host(_ptr(dvo), _ptr(v), _ptr(vb), _ptr(q), _ptr(k), _ptr(coo), _ptr(attn),
+                                        _ptr(dv), _ptr(dvb), _ptr(dq), _ptr(dk), bs, n, h, w, wv, coo.shape[0],
+                                        int(dst_mxlen), int(bool(use_softmax)), int(vb is not None), _dt(q)),
+           "l1attn_sparse_bwd_host")
+    return (dv, dq, dk) if vb is None else (dv, dvb, dq, dk)
+
+
+def expand_coo_host(co):
+    co = _np(co, np.int64).reshape(-1, 2)
+    cl = co.shape[0]
+    coo = np.zeros((cl, 4), dtype=np.int32)
+    dm, sm = _c.c_int(0), _c.c_int(0)
+    _check(lib().l1attn_expand_coo_host(_ptr(co), cl, _ptr(coo), _c.byref(dm), _c.byref(sm)),
+           "l1attn_expand_coo_host")
+    return coo, dm.value, sm.value
+
+
+# ------------------------------------------------------------------ device (torch) helpers
+
+def _tdt(t):
+    import torch
+    if t.dtype == torch.float32:
+        return F32
+    if t.dtype == torch.float64:
+        return F64
+    raise TypeError("float32 or float64 expected, got %s" % t.dtype)
+
+
+def _stream():
+    import torch
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _dp(t):
+    return None if t is None else t.data_ptr()
+
+
+def dense_fwd(q, k, out=None):
+    """q, k: contiguous CUDA tensors [bs, n, h, w].  Enqueues on the current stream."""
+    import torch
+    assert q.is_cuda and q.is_contiguous() and k.is_contiguous() and q.shape == k.shape
+    bs, n, h, w = q.shape
+    attn = torch.empty((bs, n, n, h), dtype=q.dtype, device=q.device) if out is None else out
+    _check(lib().l1attn_dense_fwd(_dp(q), _dp(k), _dp(attn), bs, n, h, w, _tdt(q), _stream()), "l1attn_dense_fwd")
+    return attn
+
+
+def dense_bwd(d_attn, q, k, out=None):
+    import torch
+    assert q.is_cuda and q.is_contiguous() and k.is_contiguous() and d_attn.is_contiguous()
+    bs, n, h, w = q.shape
+    dq, dk = (torch.empty_like(q), torch.empty_like(k)) if out is None else out
+    _check(lib().l1attn_dense_bwd(_dp(d_attn), _dp(q), _dp(k), _dp(dq), _dp(dk), bs, n, h, w, _tdt(q), _stream()),
+           "l1attn_dense_bwd")
+    return dq, dk
+
+
+class SparseIndex:
+    """Device-resident edge index of one coo tensor (see l1attn_sparse_build_index)."""
+
+    def __init__(self, coo, n_tok, dst_mxlen):
+        import torch
+        assert coo.is_cuda and coo.dtype == torch.int32 and coo.is_contiguous() and coo.shape[1] == 4
+        self.cl, self.n_tok, self.dst_mxlen = int(coo.shape[0]), int(n_tok), int(dst_mxlen)
+        nbytes = lib().l1attn_sparse_index_bytes(self.cl, self.n_tok, self.dst_mxlen)
+        self.buf = torch.empty((nbytes + 3) // 4, dtype=torch.int32, device=coo.device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=coo.device)
+        _check(lib().l1attn_sparse_build_index(_dp(coo), self.cl, self.n_tok, self.dst_mxlen, _dp(self.buf),
+                                               _dp(self.status), _stream()), "l1attn_sparse_build_index")
+
+    def check(self):
+        """Synchronises; raises if coo held an out-of-range row."""
+        _check(int(self.status.item()), "coo")
+
+
+def sparse_fwd(v, q, k, index, use_softmax=True, vb=None, out=None):
+    import torch
+    bs, n, h, w = q.shape
+    wv = v.shape[3]
+    if out is None:
+        vo = torch.empty((bs, n, h, wv), dtype=q.dtype, device=q.device)
+        attn = torch.empty((bs, n, index.dst_mxlen, h), dtype=q.dtype, device=q.device)
+    else:
+        vo, attn = out
+    _check(lib().l1attn_sparse_fwd(_dp(v), _dp(vb), _dp(q), _dp(k), _dp(index.buf), _dp(vo), _dp(attn), bs, n, h, w,
+                                   wv, index.cl, index.dst_mxlen, int(bool(use_softmax)), int(vb is not None),
+                                   _tdt(q), _stream()), "l1attn_sparse_fwd")
+    return vo, attn
+
+
+def sparse_bwd(dvo, v, q, k, index, attn, use_softmax=True, vb=None, out=None, scratch=None):
+    import torch
+    bs, n, h, w = q.shape
+    wv = v.shape[3]
+    if out is None:
+        out = (torch.empty_like(v), torch.empty_like(v) if vb is not None else None,
+               torch.empty_like(q), torch.empty_like(k))
+    dv, dvb, dq, dk = out
+    if scratch is None:
+        scratch = torch.empty_like(attn)
+    _check(lib().l1attn_sparse_bwd(_dp(dvo), _dp(v), _dp(vb), _dp(q), _dp(k), _dp(index.buf), _dp(attn), _dp(dv),
+                                   _dp(dvb), _dp(dq), _dp(dk), _dp(scratch), bs, n, h, w, wv, index.cl,
+                                   index.dst_mxlen, int(bool(use_softmax)), int(vb is not None), _tdt(q), _stream()),
+           "l1attn_sparse_bwd")
+    return (dv, dq, dk) if vb is None else (dv, dvb, dq, dk)

@@ -1,0 +1,89 @@
+"""CPU-side checks of the C ABI: the library loads, exports every function that
+include/l1attn_b200.h declares, the ctypes table covers the same set, and argument validation
+answers before any CUDA call is made (so these run on a box without a GPU)."""
+import ctypes
+import os
+import re
+
+import pytest
+
+from conftest import ROOT
+
+import l1attn_cabi
+
+HEADER = os.path.join(ROOT, "include", "l1attn_b200.h")
+
+
+def declared_functions():
+    src = open(HEADER).read()
+    src = re.sub(r"/\*.*?\*/", "", src, flags=re.S)
+    return sorted(set(re.findall(r"\b(l1attn_[a-z0-9_]+)\s*\(", src)))
+
+
+def test_header_declares_expected_surface():
+    names = declared_functions()
+    for must in ("l1attn_dense_fwd", "l1attn_dense_bwd", "l1attn_sparse_fwd", "l1attn_sparse_bwd",
+                 "l1attn_sparse_build_index", "l1attn_expand_coo", "l1attn_dense_fwd_host"):
+        assert must in names
+
+
+def test_library_exports_every_declared_symbol():
+    lib = l1attn_cabi.lib()
+    for name in declared_functions():
+        assert hasattr(lib, name), "libl1attn_b200.so does not export %s" % name
+
+
+def test_ctypes_table_matches_header():
+    assert sorted(l1attn_cabi.SIGNATURES) == declared_functions()
+
+
+def test_version_and_strerror():
+    lib = l1attn_cabi.lib()
+    assert lib.l1attn_version() >= 100
+    assert lib.l1attn_strerror(0) == b"ok"
+    for code in range(-6, 0):
+        assert b"unknown l1attn" not in lib.l1attn_strerror(code)
+    assert b"unknown l1attn" in lib.l1attn_strerror(-99)
+
+
+def test_argument_validation_needs_no_gpu():
+    lib = l1attn_cabi.lib()
+    buf = (ctypes.c_double * 16)()
+    p = ctypes.addressof(buf)
+    # negative size, unknown dtype, NULL pointer, misaligned pointer
+    assert lib.l1attn_dense_fwd(p, p, p, -1, 1, 1, 1, 0, None) == -1
+    assert lib.l1attn_dense_fwd(p, p, p, 1, 1, 1, 1, 7, None) == -1
+    assert lib.l1attn_dense_fwd(None, p, p, 1, 1, 1, 1, 0, None) == -1
+    assert lib.l1attn_dense_fwd(p + 2, p, p, 1, 1, 1, 1, 0, None) == -6
+    assert lib.l1attn_dense_bwd(p, p, p, p, None, 1, 1, 1, 1, 1, None) == -1
+    assert lib.l1attn_dense_fwd(p, p, p, 1, 1, 1, 0, 0, None) == -1  # width must be >= 1
+    assert lib.l1attn_sparse_fwd(p, None, p, p, p, p, p, 1, 1, 1, 0, 1, 1, 1, 1, 0, 0, None) == -1
+    assert lib.l1attn_sparse_fwd(p, None, p, p, None, p, p, 1, 1, 1, 1, 1, 1, 1, 1, 0, 0, None) == -1
+    assert lib.l1attn_sparse_fwd(p, None, p, p, p, p, p, 1, 1, 1, 1, 1, 1, 1, 1, 1, 0, None) == -1  # bidi without vb
+    assert lib.l1attn_sparse_build_index(None, 3, 4, 2, p, None, None) == -1
+    assert lib.l1attn_sparse_build_index(p, 1, 1 << 20, 1 << 12, p, None, None) == -2  # slot table > 2^31
+    assert lib.l1attn_expand_coo(None, 4, p, p, 0, 10, None, None) == -1
+    # empty problems are fine and touch nothing
+    assert lib.l1attn_dense_fwd(None, None, None, 0, 5, 2, 8, 0, None) == 0
+    assert lib.l1attn_dense_bwd(None, None, None, None, None, 3, 0, 2, 8, 1, None) == 0
+
+
+def test_size_queries():
+    lib = l1attn_cabi.lib()
+    assert lib.l1attn_sparse_index_bytes(0, 0, 0) >= 16
+    n = lib.l1attn_sparse_index_bytes(131072, 4096, 32)
+    assert n >= 4 * (4096 * 32 + 4097 + 131072) and n % 16 == 0
+    assert lib.l1attn_sparse_bwd_scratch_bytes(8, 4096, 8, 32, 0) == 8 * 4096 * 8 * 32 * 4
+    assert lib.l1attn_sparse_bwd_scratch_bytes(8, 4096, 8, 32, 1) == 8 * 4096 * 8 * 32 * 8
+    assert lib.l1attn_expand_coo_scratch_bytes(4096) == 0
+    assert lib.l1attn_expand_coo_scratch_bytes(1 << 20) == (1 << 20) * 8
+
+
+def test_no_cpu_fallback_in_product():
+    """The shipped package must never import the oracle."""
+    pkg = os.path.join(ROOT, "l1-attention_b200")
+    for dirpath, _, files in os.walk(pkg):
+        for f in files:
+            if f.endswith((".py", ".cu", ".cuh", ".cpp", ".h")):
+                text = open(os.path.join(dirpath, f)).read()
+                assert "oracle" not in text.lower() or f == "build.py", "%s mentions the oracle" % f

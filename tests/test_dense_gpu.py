@@ -1,0 +1,180 @@
+"""Dense L1Attn forward/backward on the GPU, through the C ABI, against the CPU oracle.
+
+Tolerances (norm-wise, see conftest.rel_err): fp64 1e-12, fp32 1e-5 -- the bars the task states.
+"""
+import numpy as np
+import pytest
+
+from conftest import assert_close
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+
+TOL = {np.float32: 1e-5, np.float64: 1e-12}
+
+SHAPES = [(1, 1, 1, 1), (1, 16, 8, 64), (2, 5, 3, 7), (1, 9, 2, 33), (2, 17, 5, 16), (1, 33, 9, 65),
+          (3, 70, 12, 32), (1, 130, 16, 64), (2, 64, 1, 128), (1, 3, 16, 7), (2, 40, 8, 97), (1, 65, 24, 64)]
+
+
+def _cabi():
+    import l1attn_cabi
+    return l1attn_cabi
+
+
+def _rand(shape, dtype, seed):
+    rng = np.random.RandomState(seed)
+    bs, n, h, w = shape
+    return (rng.standard_normal(shape).astype(dtype), rng.standard_normal(shape).astype(dtype),
+            rng.standard_normal((bs, n, n, h)).astype(dtype))
+
+
+def _dev(a):
+    return torch.from_numpy(a).cuda()
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+@pytest.mark.parametrize("shape", SHAPES)
+def test_fwd_bwd_vs_oracle(shape, dtype):
+    from oracle import oracle
+    cabi = _cabi()
+    q, k, g = _rand(shape, dtype, hash(shape) % 1000)
+    attn = cabi.dense_fwd(_dev(q), _dev(k)).cpu().numpy()
+    dq, dk = (x.cpu().numpy() for x in cabi.dense_bwd(_dev(g), _dev(q), _dev(k)))
+    # the oracle runs in fp64 on the same (fp32-representable) inputs
+    q64, k64, g64 = q.astype(np.float64), k.astype(np.float64), g.astype(np.float64)
+    assert_close(attn, oracle.dense_fwd(q64, k64), TOL[dtype], "attn %s" % (shape,))
+    rq, rk = oracle.dense_bwd(g64, q64, k64)
+    assert_close(dq, rq, TOL[dtype], "dq %s" % (shape,))
+    assert_close(dk, rk, TOL[dtype], "dk %s" % (shape,))
+
+
+def test_golden_fixtures(golden):
+    """Reference outputs (pure-PyTorch and compiled CPU extension) on seeded inputs, incl. the
+    tie-heavy and zero-padded cases: sign(0) must be exactly 0."""
+    cabi = _cabi()
+    g = golden["dense"]
+    for name in g["names"]:
+        q, k, da = g[name + "_q"], g[name + "_k"], g[name + "_dattn"]
+        attn = cabi.dense_fwd(_dev(q), _dev(k)).cpu().numpy()
+        dq, dk = (x.cpu().numpy() for x in cabi.dense_bwd(_dev(da), _dev(q), _dev(k)))
+        for ref in ("py", "cpp"):
+            if "%s_attn_%s" % (name, ref) not in g:
+                continue
+            assert_close(attn, g["%s_attn_%s" % (name, ref)], 1e-12, "%s attn vs %s" % (name, ref))
+            assert_close(dq, g["%s_dq_%s" % (name, ref)], 1e-12, "%s dq vs %s" % (name, ref))
+            assert_close(dk, g["%s_dk_%s" % (name, ref)], 1e-12, "%s dk vs %s" % (name, ref))
+        # fp32 on the same inputs
+        a32 = cabi.dense_fwd(_dev(q.astype(np.float32)), _dev(k.astype(np.float32))).cpu().numpy()
+        assert_close(a32, g[name + "_attn_py"], 1e-5, name + " attn fp32")
+
+
+def test_kat(golden):
+    cabi = _cabi()
+    g = golden["kat"]
+    a = cabi.dense_fwd(_dev(g["f3_q"]), _dev(g["f3_k"])).cpu().numpy()
+    expect = np.array([[-1, -1, 0, -.5], [0, -1, -1, -.5], [-1, 0, -1, -.5], [-.5, -.5, -.5, 0]], dtype=np.float32)
+    assert np.array_equal(a[0, :, :, 0], expect)
+    a1 = cabi.dense_fwd(_dev(g["f1_q"]), _dev(g["f1_k"])).cpu().numpy()
+    assert_close(a1, g["f1_dense_attn"], 1e-6, "f1")
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+def test_ties_exact(dtype):
+    """Inputs on a coarse grid: every difference and every sum is exact in fp32, so the GPU
+    result must equal the oracle bit for bit up to the final scale multiply, and rows with
+    q == k must contribute exactly nothing."""
+    from oracle import oracle
+    cabi = _cabi()
+    rng = np.random.RandomState(5)
+    shape = (2, 48, 8, 64)
+    q = (np.round(rng.standard_normal(shape) * 2) / 2).astype(dtype)
+    k = (np.round(rng.standard_normal(shape) * 2) / 2).astype(dtype)
+    k[:, 40:] = q[:, 40:]  # identical rows
+    q[:, 44:] = 0
+    k[:, 44:] = 0  # zero padding
+    g = np.round(rng.standard_normal((2, 48, 48, 8)) * 4).astype(dtype) / 4
+    dq, dk = (x.cpu().numpy() for x in cabi.dense_bwd(_dev(g), _dev(q), _dev(k)))
+    rq, rk = oracle.dense_bwd(g.astype(np.float64), q.astype(np.float64), k.astype(np.float64))
+    assert_close(dq, rq, 2e-7 if dtype == np.float32 else 1e-14, "dq ties")
+    assert_close(dk, rk, 2e-7 if dtype == np.float32 else 1e-14, "dk ties")
+
+
+def test_deterministic():
+    cabi = _cabi()
+    q, k, g = _rand((2, 96, 16, 64), np.float32, 11)
+    a = [cabi.dense_bwd(_dev(g), _dev(q), _dev(k)) for _ in range(2)]
+    assert torch.equal(a[0][0], a[1][0]) and torch.equal(a[0][1], a[1][1])
+    f = [cabi.dense_fwd(_dev(q), _dev(k)) for _ in range(2)]
+    assert torch.equal(f[0], f[1])
+
+
+def test_host_buffer_entry_points():
+    from oracle import oracle
+    cabi = _cabi()
+    q, k, g = _rand((2, 37, 5, 24), np.float32, 3)
+    attn = cabi.dense_fwd_host(q, k)
+    dq, dk = cabi.dense_bwd_host(g, q, k)
+    q64, k64, g64 = q.astype(np.float64), k.astype(np.float64), g.astype(np.float64)
+    assert_close(attn, oracle.dense_fwd(q64, k64), 1e-5, "host attn")
+    rq, rk = oracle.dense_bwd(g64, q64, k64)
+    assert_close(dq, rq, 1e-5, "host dq")
+    assert_close(dk, rk, 1e-5, "host dk")
+    assert cabi.lib().l1attn_host_release() == 0
+
+
+def test_fp64_long_context_variant_full():
+    """BASELINE's fp64 variant [2,512,8,128], checked in full against the oracle at 1e-12."""
+    from oracle import oracle
+    cabi = _cabi()
+    rng = np.random.RandomState(3001)
+    shape = (2, 512, 8, 128)
+    q, k = rng.standard_normal(shape), rng.standard_normal(shape)
+    g = rng.standard_normal((2, 512, 512, 8))
+    attn = cabi.dense_fwd(_dev(q), _dev(k)).cpu().numpy()
+    dq, dk = (x.cpu().numpy() for x in cabi.dense_bwd(_dev(g), _dev(q), _dev(k)))
+    assert_close(attn, oracle.dense_fwd(q, k), 1e-12, "attn")
+    rq, rk = oracle.dense_bwd(g, q, k)
+    assert_close(dq, rq, 1e-12, "dq")
+    assert_close(dk, rk, 1e-12, "dk")
+
+
+@pytest.mark.parametrize("shape", [(16, 1024, 16, 64), (2, 4096, 8, 128)])
+def test_full_size_properties(shape):
+    """BASELINE's fp32 benchmark shapes, too large for the oracle: size-independent properties.
+      * swapping q and k transposes the score matrix exactly (|q-k| is symmetric);
+      * sampled (b, s, t) entries and sampled gradient rows match a float64 numpy evaluation;
+      * the backward is linear in d_attn."""
+    cabi = _cabi()
+    bs, n, h, w = shape
+    gen = torch.Generator(device="cuda").manual_seed(2000)
+    q = torch.randn(shape, generator=gen, device="cuda")
+    k = torch.randn(shape, generator=gen, device="cuda")
+    attn = cabi.dense_fwd(q, k)
+    attn_sw = cabi.dense_fwd(k, q)
+    assert torch.equal(attn, attn_sw.transpose(1, 2))
+    del attn_sw
+    scale = -1.0 / np.sqrt(w)
+    rng = np.random.RandomState(7)
+    qh, kh = q.double().cpu().numpy(), k.double().cpu().numpy()
+    for _ in range(64):
+        b, s, t = rng.randint(bs), rng.randint(n), rng.randint(n)
+        ref = scale * np.abs(qh[b, t] - kh[b, s]).sum(-1)
+        assert_close(attn[b, s, t].cpu().numpy(), ref, 1e-5, "sample attn")
+    g1 = torch.randn(attn.shape, generator=gen, device="cuda")
+    dq1, dk1 = cabi.dense_bwd(g1, q, k)
+    for _ in range(8):
+        b, t = rng.randint(bs), rng.randint(n)
+        sg = np.sign(qh[b, t][None] - kh[b])  # [s, h, w]
+        ref = scale * (sg * g1[b, :, t].double().cpu().numpy()[:, :, None]).sum(0)
+        assert_close(dq1[b, t].cpu().numpy(), ref, 1e-5, "sample dq")
+        s = rng.randint(n)
+        sg = np.sign(qh[b] - kh[b, s][None])  # [t, h, w]
+        ref = -scale * (sg * g1[b, s].double().cpu().numpy()[:, :, None]).sum(0)
+        assert_close(dk1[b, s].cpu().numpy(), ref, 1e-5, "sample dk")
+    g2 = torch.randn(attn.shape, generator=gen, device="cuda")
+    dq2, dk2 = cabi.dense_bwd(g2, q, k)
+    g1.add_(g2)
+    del g2
+    dq3, dk3 = cabi.dense_bwd(g1, q, k)
+    assert_close((dq1 + dq2).cpu().numpy(), dq3.cpu().numpy(), 1e-5, "linearity dq")
+    assert_close((dk1 + dk2).cpu().numpy(), dk3.cpu().numpy(), 1e-5, "linearity dk")

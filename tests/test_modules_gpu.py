@@ -1,0 +1,182 @@
+"""The reference-facing Python / pybind surface: module and class names, call signatures,
+autograd, error behaviour -- written after the reference's own check scripts (check.py,
+check_sparse.py), with the oracle in place of its CPU extension."""
+import numpy as np
+import pytest
+
+from conftest import assert_close
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+
+
+def test_dense_module_forward_backward_gradcheck():
+    from oracle import oracle
+    import l1attn_cuda
+    torch.manual_seed(1)
+    q = torch.randn(1, 16, 8, 64, dtype=torch.float64, device="cuda", requires_grad=True)  # check.py:17-22
+    k = torch.randn(1, 16, 8, 64, dtype=torch.float64, device="cuda", requires_grad=True)
+    attn = l1attn_cuda.L1Attn()(q, k)
+    assert attn.shape == (1, 16, 16, 8)
+    assert_close(attn.detach().cpu().numpy(), oracle.dense_fwd(q.detach().cpu().numpy(), k.detach().cpu().numpy()), 1e-12)
+    q2 = torch.randn(2, 5, 3, 7, dtype=torch.float64, device="cuda", requires_grad=True)
+    k2 = torch.randn(2, 5, 3, 7, dtype=torch.float64, device="cuda", requires_grad=True)
+    assert torch.autograd.gradcheck(l1attn_cuda.L1AttnFn.apply, (q2, k2), eps=1e-6, atol=1e-4, nondet_tol=1e-6)
+    # the usual consumer: softmax over dim 1, einsum with v (README.md:64-66); non-contiguous grads arrive here
+    v = torch.randn(1, 16, 8, 64, dtype=torch.float64, device="cuda")
+    vo = torch.einsum("bsdh,bshw->bdhw", torch.softmax(attn, 1), v)
+    vo.sum().backward()
+    assert q.grad is not None and torch.isfinite(q.grad).all()
+
+
+def test_dense_driver_surface_and_errors():
+    import l1attn_cuda_drv
+    q = torch.randn(1, 4, 2, 8, device="cuda")
+    out = l1attn_cuda_drv.forward(q, q)
+    assert isinstance(out, list) and len(out) == 1
+    dq, dk = l1attn_cuda_drv.backward(torch.ones_like(out[0]), q, q)
+    assert dq.shape == q.shape and dk.shape == q.shape
+    with pytest.raises(RuntimeError, match="must be a CUDA tensor"):
+        l1attn_cuda_drv.forward(q.cpu(), q)
+    with pytest.raises(RuntimeError, match="must be contiguous"):
+        l1attn_cuda_drv.forward(q.transpose(1, 2), q)
+    with pytest.raises(RuntimeError):
+        l1attn_cuda_drv.forward(q, q[:, :2].contiguous())
+    with pytest.raises(RuntimeError):
+        l1attn_cuda_drv.forward(q.half(), q.half())
+
+
+def test_dense_on_non_default_stream():
+    import l1attn_cuda
+    q = torch.randn(2, 64, 8, 32, device="cuda")
+    k = torch.randn(2, 64, 8, 32, device="cuda")
+    ref = l1attn_cuda.L1Attn()(q, k)
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        out = l1attn_cuda.L1Attn()(q, k)
+    s.synchronize()
+    assert torch.equal(out, ref)
+
+
+@pytest.mark.parametrize("usm", [True, False])
+def test_sparse_modules_vs_oracle_and_gradcheck(usm):
+    """check_sparse.py's ladder: cartesian, permuted, permuted with rows dropped."""
+    from oracle import oracle
+    import l1attn_sparse_cuda
+    import l1attn_sparse_bidi_cuda
+    torch.manual_seed(2)
+    bs, n, h, w = 2, 3, 16, 7  # check_sparse.py:18-21
+    base = torch.cartesian_prod(torch.arange(n), torch.arange(n))
+    for co in (base, base[torch.randperm(9)], base[torch.randperm(9)][:-4]):
+        coo, dm, sm = l1attn_sparse_cuda.expandCoo(co)
+        rcoo, rdm, rsm = oracle.expand_coo(co.numpy())
+        assert coo.dtype == torch.int32 and coo.device == co.device
+        assert np.array_equal(coo.numpy(), rcoo) and (dm, sm) == (rdm, rsm)
+        coo2, dm2, sm2 = l1attn_sparse_bidi_cuda.expandCoo(co.cuda())
+        assert coo2.is_cuda and np.array_equal(coo2.cpu().numpy(), rcoo)
+        coo = coo.cuda()
+        mk = lambda: torch.randn(bs, n, h, w, dtype=torch.float64, device="cuda", requires_grad=True)
+        v, vb, q, k = mk(), mk(), mk(), mk()
+        vo = l1attn_sparse_cuda.L1AttnSparse()(v, q, k, coo, dm, usm)
+        rvo, _ = oracle.sparse_fwd(*(x.detach().cpu().numpy() for x in (v, q, k)), rcoo, dm, usm)
+        assert_close(vo.detach().cpu().numpy(), rvo, 1e-12)
+        bvo = l1attn_sparse_bidi_cuda.L1AttnSparseBidi()(v, vb, q, k, coo, dm, usm)
+        rbvo, _ = oracle.sparse_bidi_fwd(*(x.detach().cpu().numpy() for x in (v, vb, q, k)), rcoo, dm, usm)
+        assert_close(bvo.detach().cpu().numpy(), rbvo, 1e-12)
+        f = lambda v_, q_, k_: l1attn_sparse_cuda.L1AttnSparseFn.apply(v_, q_, k_, coo, dm, usm)
+        assert torch.autograd.gradcheck(f, (v, q, k), eps=1e-6, atol=1e-4, nondet_tol=1e-6)
+        fb = lambda a, b, c, d: l1attn_sparse_bidi_cuda.L1AttnSparseBidiFn.apply(a, b, c, d, coo, dm, usm)
+        assert torch.autograd.gradcheck(fb, (v, vb, q, k), eps=1e-6, atol=1e-4, nondet_tol=1e-6)
+
+
+def test_sparse_five_argument_call_defaults_to_softmax():
+    import l1attn_sparse_cuda
+    co = torch.tensor([[0, 0], [0, 1], [1, 0], [1, 1], [2, 2]])
+    coo, dm, _ = l1attn_sparse_cuda.expandCoo(co)
+    t = [torch.randn(1, 3, 2, 8, device="cuda", requires_grad=True) for _ in range(3)]
+    m = l1attn_sparse_cuda.L1AttnSparse()
+    a = m(*t, coo.cuda(), dm)           # README.md:93 form
+    b = m(*t, coo.cuda(), dm, True)     # testsparse.py:27 form
+    assert torch.equal(a, b)
+    l1attn_sparse_cuda.L1AttnSparseFn.apply(*t, coo.cuda(), dm).sum().backward()
+    assert t[0].grad is not None
+
+
+def test_sparse_driver_errors():
+    import l1attn_sparse_cuda_drv as drv
+    q = torch.randn(1, 3, 2, 8, device="cuda")
+    coo = torch.tensor([[0, 1, 0, 0]], dtype=torch.int32, device="cuda")
+    vo, attn = drv.forward(q, q, q, coo, 1, True)
+    assert vo.shape == q.shape and attn.shape == (1, 3, 1, 2)
+    with pytest.raises(RuntimeError, match="must be a CUDA tensor"):
+        drv.forward(q, q, q, coo.cpu(), 1, True)
+    with pytest.raises(RuntimeError, match="int32"):
+        drv.forward(q, q, q, coo.long(), 1, True)
+    bad = torch.tensor([[0, 7, 0, 0]], dtype=torch.int32, device="cuda")
+    with pytest.raises(RuntimeError, match="coo"):
+        drv.forward(q, q, q, bad, 1, True)
+
+
+def test_index_cache_sees_in_place_edits():
+    import l1attn_sparse_cuda_drv as drv
+    q = torch.randn(1, 4, 1, 8, device="cuda")
+    coo = torch.tensor([[0, 1, 0, 0], [2, 3, 0, 0]], dtype=torch.int32, device="cuda")
+    a, _ = drv.forward(q, q, q, coo, 1, False)
+    coo[0, 1] = 2  # same storage, new graph
+    b, _ = drv.forward(q, q, q, coo, 1, False)
+    assert not torch.equal(a[0, 0], b[0, 0])
+
+
+def _ref_cuda(name):
+    import importlib
+    import os
+    import sys
+    from conftest import ROOT
+    d = os.path.join(ROOT, "oracle", "_ref")
+    if not os.path.exists(os.path.join(d, name + ".so")):
+        pytest.skip("reference GPU extension not built (oracle/build_ref.py)")
+    if d not in sys.path:
+        sys.path.insert(0, d)
+    return importlib.import_module(name)
+
+
+def test_dense_fp32_vs_reference_cuda():
+    """fp32 within 1e-5 of the reference's own GPU kernels (rebuilt for sm_100) on the same inputs."""
+    ref = _ref_cuda("ref_l1attn_cuda_drv")
+    import l1attn_cuda_drv as new
+    torch.manual_seed(5)
+    for shape in ((2, 64, 8, 64), (1, 48, 4, 32), (2, 20, 3, 33)):  # w==64, w%32==0 and generic reference paths
+        q = torch.randn(shape, device="cuda")
+        k = torch.randn(shape, device="cuda")
+        g = torch.randn(shape[0], shape[1], shape[1], shape[2], device="cuda")
+        assert_close(new.forward(q, k)[0].cpu().numpy(), ref.forward(q, k)[0].cpu().numpy(), 1e-5, "attn")
+        for x, r in zip(new.backward(g, q, k), ref.backward(g, q, k)):
+            assert_close(x.cpu().numpy(), r.cpu().numpy(), 1e-5, "grad")
+
+
+@pytest.mark.parametrize("usm", [True, False])
+def test_sparse_fp32_vs_reference_cuda(usm):
+    ref = _ref_cuda("ref_l1attn_sparse_cuda_drv")
+    refb = _ref_cuda("ref_l1attn_sparse_bidi_cuda_drv")
+    import l1attn_sparse_cuda_drv as new
+    import l1attn_sparse_bidi_cuda_drv as newb
+    from test_sparse_gpu import bench_graph
+    from oracle import oracle
+    coo, dm, _ = oracle.expand_coo(bench_graph(256, 15, 5))
+    coo = torch.from_numpy(coo).cuda()
+    gen = torch.Generator(device="cuda").manual_seed(6)
+    q, k = (0.25 * torch.randn(2, 256, 8, 64, device="cuda", generator=gen) for _ in range(2))
+    v, vb, dvo = (torch.randn(2, 256, 8, 64, device="cuda", generator=gen) for _ in range(3))
+    vo, attn = new.forward(v, q, k, coo, dm, usm)
+    rvo, rattn = ref.forward(v, q, k, coo, dm, usm)
+    assert_close(vo.cpu().numpy(), rvo.cpu().numpy(), 1e-5, "vo")
+    assert_close(attn.cpu().numpy(), rattn.cpu().numpy(), 1e-5, "attn")
+    for x, r in zip(new.backward(dvo, v, q, k, coo, attn, dm, usm), ref.backward(dvo, v, q, k, coo, rattn, dm, usm)):
+        assert_close(x.cpu().numpy(), r.cpu().numpy(), 1e-5, "grad")
+    vo, attn = newb.forward(v, vb, q, k, coo, dm, usm)
+    rvo, rattn = refb.forward(v, vb, q, k, coo, dm, usm)
+    assert_close(vo.cpu().numpy(), rvo.cpu().numpy(), 1e-5, "bidi vo")
+    for x, r in zip(newb.backward(dvo, v, vb, q, k, coo, attn, dm, usm),
+                    refb.backward(dvo, v, vb, q, k, coo, rattn, dm, usm)):
+        assert_close(x.cpu().numpy(), r.cpu().numpy(), 1e-5, "bidi grad")
