@@ -39,6 +39,8 @@ WORKLOADS = {
     "dense_cfg2": dict(kind="dense", shape=(16, 1024, 16, 64)),
     "dense_cfg3": dict(kind="dense", shape=(2, 4096, 8, 128)),
     "dense_cfg1": dict(kind="dense", shape=(4, 128, 8, 64)),
+    "dense_small": dict(kind="dense", shape=(2, 1024, 16, 64)),  # profiling size: 134 MB of scores, > L2
+    "sparse_small": dict(kind="sparse", shape=(2, 4096, 8, 64), fan=31),
     "sparse_cfg4": dict(kind="sparse", shape=(8, 4096, 8, 64), fan=31),
 }
 SM_COUNT, FP32_LANES = 148, 128
@@ -271,11 +273,11 @@ def run_ours(args, wl):
             dist.barrier()
             torch.cuda.synchronize()
 
+    sampler = ClockSampler(local) if rank == 0 else None
     for _ in range(max(args.warmup, 3)):
         fwd()
         bwd()
     sync_all()
-    sampler = ClockSampler(local) if rank == 0 else None
     ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
     t_wall0 = time.time()
     for i in range(args.steps):
@@ -299,7 +301,12 @@ def run_ours(args, wl):
 
     # ---- end to end through the host-buffer C ABI (rank-local; max over ranks)
     e2e_steps = max(1, min(args.steps, 3))
-    if kind == "dense":
+    if args.kernel_only:
+        h2d = d2h = 0
+
+        def e2e_step():
+            return 0.0
+    elif kind == "dense":
         hq, hk = (torch.randn(shape).pin_memory() for _ in range(2))
         hg = torch.randn((bs, n, n, h)).pin_memory()
         hattn = torch.empty((bs, n, n, h)).pin_memory()
@@ -357,7 +364,7 @@ def run_ours(args, wl):
             roof["frac"] = roof["achieved"] / roof["peak"]
             alu = None
         cpu = None
-        if world == 1 and not args.no_cpu_baseline:
+        if world == 1 and not args.no_cpu_baseline and not args.kernel_only:
             r, info = cpu_reference_rate(kind, shape, 15.0, wl.get("fan", 31))
             cpu = dict(value=r, unit=unit, cores=info["cores"], kind=info["kind"], sample=info["sample"])
         line = {
@@ -384,6 +391,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="dense_cfg2", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--kernel-only", action="store_true", help="skip the end-to-end and CPU legs (profiling runs)")
     args = ap.parse_args()
     wl = WORKLOADS[args.workload]
     if args.impl == "reference":

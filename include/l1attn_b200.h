@@ -41,6 +41,7 @@ extern "C" {
 #define L1ATTN_ERR_INDEX (-4)    /* coo holds a token / rank outside [0,n_tok) / [0,dst_mxlen) */
 #define L1ATTN_ERR_NOMEM (-5)    /* host-buffer entry point could not get device memory */
 #define L1ATTN_ERR_ALIGN (-6)    /* a floating tensor pointer is not aligned to its element size */
+#define L1ATTN_ERR_TIMEOUT (-7)  /* a kernel gave up a bounded wait on an asynchronous copy (its output is invalid) */
 
 #define L1ATTN_F32 0
 #define L1ATTN_F64 1
@@ -51,6 +52,12 @@ int l1attn_version(void);
 const char *l1attn_strerror(int code);
 /* cudaError_t (as int) of the last failing CUDA call made by this library on this thread, 0 if none. */
 int l1attn_last_cuda_error(void);
+/*
+ * Synchronises with the device and reports whether any kernel of this library gave up a bounded
+ * wait since the last call (L1ATTN_ERR_TIMEOUT, cleared by the call) -- the kernels that stage
+ * tiles with asynchronous bulk copies never spin without a limit.  L1ATTN_OK otherwise.
+ */
+int l1attn_device_status(void);
 
 /* ------------------------------------------------------------------ dense --------------- */
 

@@ -66,6 +66,9 @@ template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile(
 // Launchers implemented per file; all return an L1ATTN_* status and never synchronise.
 int dense_fwd_launch(const void *q, const void *k, void *attn, int bs, int n_tok, int n_heads, int width,
 		     int dtype, cudaStream_t st);
+// fast paths: return 1 when they do not apply to the given shape / alignment / device
+int dense_fwd_tma_launch(const void *q, const void *k, void *attn, int bs, int n_tok, int n_heads, int width,
+			 int dtype, cudaStream_t st);
 int dense_bwd_launch(const void *d_attn, const void *q, const void *k, void *d_q, void *d_k, int bs, int n_tok,
 		     int n_heads, int width, int dtype, cudaStream_t st);
 

@@ -9,6 +9,7 @@
 // 16-byte shared-memory read feeds TN (resp. TM) x 4 abs-difference terms.
 // Shared memory is XOR-swizzled on the 16-byte chunk index so the 8 head-lanes hit 8 different
 // bank groups.
+#include <cstdlib>
 #include "common.cuh"
 
 namespace l1b {
@@ -156,6 +157,12 @@ int dense_fwd_launch(const void *q, const void *k, void *attn, int bs, int n_tok
 {
 	if (bs == 0 || n_tok == 0 || n_heads == 0)
 		return L1ATTN_OK;
+	static const bool no_tma = getenv("L1ATTN_NO_TMA") != nullptr; // debugging aid: force the generic kernel
+	if (!no_tma) {
+		const int rc = dense_fwd_tma_launch(q, k, attn, bs, n_tok, n_heads, width, dtype, st);
+		if (rc <= 0)
+			return rc;
+	}
 	if (dtype == L1ATTN_F32)
 		return launch<float, 8, 8, 8>((const float *)q, (const float *)k, (float *)attn, bs, n_tok, n_heads, width, st);
 	return launch<double, 4, 4, 8>((const double *)q, (const double *)k, (double *)attn, bs, n_tok, n_heads, width, st);

@@ -1,0 +1,77 @@
+// TMA (cp.async.bulk.tensor) and mbarrier helpers for sm_100a, plus host-side tensor-map encoding.
+//
+// Rules kept here:
+//  * loads only, never multicast, always from this GPU's own memory;
+//  * the innermost coordinate of every copy is a multiple of 16 bytes (callers pass width
+//    offsets that are multiples of the 64-byte stage row, and 0 for the head/row axes that are
+//    innermost in their tensors);
+//  * every wait is bounded: after WAIT_LIMIT failed polls the waiter records an error code in
+//    the device error word and gives up, so a lost copy can never hang the GPU.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace l1b {
+
+// Address (on the current device) of the sticky error word: 0 = no error; a kernel whose bounded
+// wait ran out stores a non-zero code there.  Read and cleared by l1attn_device_status().
+int *device_error_word();
+
+constexpr uint32_t WAIT_LIMIT = 1u << 24; // polls; each try_wait itself blocks for a hardware time slice
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count)
+{
+	asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_fence_init()
+{
+	asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes)
+{
+	asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar)
+{
+	asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// true when the phase with the given parity has completed; false after WAIT_LIMIT polls
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, int *err)
+{
+	const uint32_t a = smem_u32(bar);
+	for (uint32_t i = 0; i < WAIT_LIMIT; i++) {
+		uint32_t ok;
+		asm volatile("{\n\t.reg .pred p;\n\t"
+			     "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+			     "selp.u32 %0, 1, 0, p;\n\t}"
+			     : "=r"(ok)
+			     : "r"(a), "r"(parity)
+			     : "memory");
+		if (ok)
+			return true;
+	}
+	*err = 1;
+	return false;
+}
+
+// 4-D tiled load global -> shared, completion signalled on `bar` (no multicast)
+__device__ __forceinline__ void tma_load_4d(void *dst, const CUtensorMap *map, uint64_t *bar, int c0, int c1, int c2, int c3)
+{
+	asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+		     :
+		     : "r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+		     : "memory");
+}
+
+// ---- host side -----------------------------------------------------------------------------
+
+// Encodes a 4-D tiled tensor map.  dims/box are innermost-first; strides_bytes has 3 entries (dims 1..3).
+// Returns false when the driver entry point is missing or the encode call is refused (the
+// caller then uses the kernel that needs no tensor map).
+bool encode_tmap_4d(CUtensorMap *out, CUtensorMapDataType dt, const void *base, const uint64_t dims[4],
+		    const uint64_t strides_bytes[3], const uint32_t box[4], CUtensorMapSwizzle swz);
+
+} // namespace l1b

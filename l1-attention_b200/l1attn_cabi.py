@@ -24,6 +24,7 @@ SIGNATURES = {
     "l1attn_version": (_i, []),
     "l1attn_strerror": (_c.c_char_p, [_i]),
     "l1attn_last_cuda_error": (_i, []),
+    "l1attn_device_status": (_i, []),
     "l1attn_dense_fwd": (_i, [_vp] * 3 + [_i] * 5 + [_vp]),
     "l1attn_dense_bwd": (_i, [_vp] * 5 + [_i] * 5 + [_vp]),
     "l1attn_sparse_index_bytes": (_sz, [_i] * 3),
