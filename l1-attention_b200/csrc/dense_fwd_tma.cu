@@ -2,19 +2,25 @@
 //
 //   attn[b][s][t][h] = scale * sum_w |q[b][t][h][w] - k[b][s][h][w]|
 //
-// Persistent kernel: one CTA of 16 warps per SM walks a list of (batch, head-group of 8, query
-// tile of 64, key tile of 64) work items.
-//   * operands arrive by TMA tensor copies (cp.async.bulk.tensor, no multicast): per stage the
-//     64-byte-wide width chunk of the q tile and of the k tile, as [token][head][16 B chunk] boxes
-//     with the 64-byte hardware swizzle, into a ring of NSTAGE shared-memory stages, each guarded
-//     by a full/empty mbarrier pair.  One lane issues them NSTAGE-1 chunks ahead of the math and
-//     runs on across work items, so the next item's tiles land while the current one is reduced;
-//   * every warp computes: lanes = 8 heads x 4 query rows, each thread keeps an 8 x 8 (query, key)
+// Persistent, warp-specialised kernel: one CTA per SM walks a list of (batch, head-group of 8,
+// query tile of 64, key tile of 32) work items.
+//   * warp 8 is the producer: one lane issues TMA tensor copies (cp.async.bulk.tensor, no
+//     multicast) -- per stage the 64-byte-wide width chunk of the q tile and of the k tile, as
+//     [token][head][16 B chunk] boxes with the 64-byte hardware swizzle -- into a ring of NSTAGE
+//     shared-memory stages, each guarded by a full/empty mbarrier pair.  It runs ahead across
+//     work items, so the next item's tiles land while the current one is still being reduced;
+//   * warps 0..7 compute: lanes = 8 heads x 4 query rows, each thread keeps an 8 x 8 (query, key)
 //     register tile of its head, reads operands with conflict-free 16-byte shared loads (the
 //     swizzle spreads the 8 head-lanes over 8 bank groups) and spends 2 FP32 instructions per
-//     term (subtract; add with |.| as a source modifier);
-//   * the 8 head-lanes write 32 contiguous bytes per (s, t), so every store of a warp fills
-//     whole sectors of the heads-innermost output, and no [b,h,t,w] copy of q/k is ever made.
+//     term (subtract; add with |.| as a source modifier).  Eight compute warps with ~160
+//     registers each (no spills) measured faster than sixteen with 128;
+//   * results leave through shared memory: the compute warps drop their scaled tiles into a
+//     [key][query][head] staging buffer (each warp store is one 128-byte row) and one thread issues
+//     a single TMA tensor store of the 32 x 64 x 8 box; scattered 4-byte global stores from the
+//     register tiles cost over 20 % of the kernel when measured.  When the head count is not a
+//     multiple of 4 (row pitch not 16-byte aligned) the tiles are stored directly instead: the 8
+//     head-lanes then write 32 contiguous bytes per (s, t), whole sectors either way;
+//   * no [b,h,t,w] copy of q/k is ever made (the reference transposes both first).
 // Out-of-range rows/heads/width are zero-filled by TMA (|0-0| adds nothing) and masked at the store.
 // Every mbarrier wait is bounded (tma.cuh); on a timeout the CTA stops and the error word is set.
 #include "common.cuh"
@@ -26,22 +32,23 @@ namespace {
 constexpr int HG = 8;       // heads per work item
 constexpr int LT = 4;       // lanes along the query axis
 constexpr int CH = 4;       // 16-byte chunks per (token, head) row per stage
-constexpr int NCW = 16;     // consumer warps
+constexpr int NCW = 8;      // compute warps: 2 (query halves) x 4 (key groups)
 constexpr int NSTAGE = 3;
-constexpr int TT = 64, TS = 64;
+constexpr int TT = 64, TS = 32;
 constexpr int TM = 8, TN = 8;
-constexpr int STAGE_BYTES = (TT + TS) * HG * CH * 16; // 65536
-constexpr int NTHREADS = NCW * 32;
+constexpr int Q_BYTES = TT * HG * CH * 16, K_BYTES = TS * HG * CH * 16;
+constexpr int STAGE_BYTES = Q_BYTES + K_BYTES; // 49152
+constexpr int OUT_BYTES = TS * TT * HG * 4;      // 65536: staging tile [s][t][h] of the TMA store
+constexpr int NTHREADS = (NCW + 1) * 32;
 
 struct Work {
-	int ntt, nst, nhg;
-	long long total;
+	unsigned ntt, nst, nhg, total;
 };
 
 struct Item {
 	int t0, s0, h0, b;
 };
-__device__ __forceinline__ Item decode_item(const Work &wk, long long r)
+__device__ __forceinline__ Item decode_item(const Work &wk, unsigned r)
 {
 	Item x;
 	x.t0 = int(r % wk.ntt) * TT;
@@ -56,7 +63,7 @@ __device__ __forceinline__ Item decode_item(const Work &wk, long long r)
 template <typename T>
 __global__ void __launch_bounds__(NTHREADS, 1)
 dense_fwd_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kmap,
-		     T *__restrict__ attn, int n_tok, int n_heads, int width, T scale, Work wk, int *err)
+		     const __grid_constant__ CUtensorMap omap, int tma_store, T *__restrict__ attn, int n_tok, int n_heads, int width, T scale, Work wk, int *err)
 {
 	constexpr int VEC = 16 / sizeof(T);
 	constexpr int WC = CH * VEC;
@@ -76,42 +83,41 @@ dense_fwd_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_cons
 	__syncthreads();
 
 	const int nchunk = (width + WC - 1) / WC;
-	const bool issuer = tid == 0;
 
-	// issuing side: a cursor (p_item, p_ci, p_it) that runs NSTAGE-1 chunks ahead of the math
-	long long p_item = blockIdx.x;
-	int p_ci = 0;
-	uint32_t p_it = 0;
-	bool dead = false;
-	auto issue_one = [&]() {
-		if (p_item >= wk.total)
-			return;
-		const int st = p_it % NSTAGE;
-		if (!mbar_wait(&empty_bar[st], ((p_it / NSTAGE) & 1) ^ 1, err)) {
-			dead = true;
-			return;
+	if (warp == NCW) {
+		// ---------------- producer warp: one lane feeds the ring
+		if (lane == 0) {
+			int st = 0;
+			uint32_t ph = 1; // a fresh barrier reads as "previous phase (parity 1) complete"
+			for (unsigned item = blockIdx.x; item < wk.total; item += gridDim.x) {
+				const Item x = decode_item(wk, item);
+				for (int ci = 0; ci < nchunk; ci++) {
+					if (!mbar_wait(&empty_bar[st], ph, err))
+						return;
+					unsigned char *dst = stages + size_t(st) * STAGE_BYTES;
+					mbar_expect_tx(&full_bar[st], STAGE_BYTES);
+					tma_load_4d(dst, &qmap, &full_bar[st], ci * WC, x.h0, x.t0, x.b);
+					tma_load_4d(dst + Q_BYTES, &kmap, &full_bar[st], ci * WC, x.h0, x.s0, x.b);
+					if (++st == NSTAGE) {
+						st = 0;
+						ph ^= 1;
+					}
+				}
+			}
 		}
-		const Item x = decode_item(wk, p_item);
-		unsigned char *dst = stages + size_t(st) * STAGE_BYTES;
-		mbar_expect_tx(&full_bar[st], STAGE_BYTES);
-		tma_load_4d(dst, &qmap, &full_bar[st], p_ci * WC, x.h0, x.t0, x.b);
-		tma_load_4d(dst + TT * HG * CH * 16, &kmap, &full_bar[st], p_ci * WC, x.h0, x.s0, x.b);
-		p_it++;
-		if (++p_ci == nchunk) {
-			p_ci = 0;
-			p_item += gridDim.x;
-		}
-	};
-	if (issuer)
-		for (int i = 0; i < NSTAGE - 1; i++)
-			issue_one();
+		return;
+	}
 
+	// ---------------- compute warps
 	const int lane_h = lane & 7, lane_t = lane >> 3;
-	const int wt = warp & 1, ws = warp >> 1; // 2 query halves x 8 key groups
+	const int wt = warp & 1, ws = warp >> 1; // 2 query halves x 4 key groups
 	const int sw = (lane_h >> 1) & 3;        // TMA 64-byte swizzle: chunk ^= address bits 7..8 = (head >> 1) & 3
-	uint32_t it = 0;
-	for (long long item = blockIdx.x; item < wk.total; item += gridDim.x) {
-		const Item x = decode_item(wk, item);
+	const int qoff = ((wt * 32 + lane_t) * HG + lane_h) * CH;
+	const int koff = Q_BYTES / 16 + ((ws * TN) * HG + lane_h) * CH;
+	int st = 0;
+	uint32_t ph = 0;
+	bool dead = false;
+	for (unsigned item = blockIdx.x; item < wk.total; item += gridDim.x) {
 		T acc[TM][TN];
 #pragma unroll
 		for (int i = 0; i < TM; i++)
@@ -119,20 +125,13 @@ dense_fwd_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_cons
 			for (int j = 0; j < TN; j++)
 				acc[i][j] = T(0);
 
-		for (int ci = 0; ci < nchunk; ci++, it++) {
-			if (issuer) {
-				issue_one(); // refills the stage that every warp released after chunk it-1
-				if (dead)
-					return;
-			}
-			__syncwarp();
-			const int st = it % NSTAGE;
-			if (!mbar_wait(&full_bar[st], (it / NSTAGE) & 1, err))
-				return;
-			const V *Q = reinterpret_cast<const V *>(stages + size_t(st) * STAGE_BYTES);
-			const V *K = Q + TT * HG * CH;
-			const V *qp = Q + ((wt * 32 + lane_t) * HG + lane_h) * CH;
-			const V *kp = K + ((ws * TN) * HG + lane_h) * CH;
+		for (int ci = 0; ci < nchunk; ci++) {
+			// after a timeout the warp keeps walking its items without waiting (results are
+			// invalid and the error word says so) so that it still meets the others at the barriers
+			if (!dead && !mbar_wait(&full_bar[st], ph, err))
+				dead = true;
+			const V *S = reinterpret_cast<const V *>(stages + size_t(st) * STAGE_BYTES);
+			const V *qp = S + qoff, *kp = S + koff;
 #pragma unroll
 			for (int c = 0; c < CH; c++) {
 				const int pc = c ^ sw;
@@ -153,8 +152,32 @@ dense_fwd_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_cons
 			__syncwarp();
 			if (lane == 0)
 				mbar_arrive(&empty_bar[st]);
+			if (++st == NSTAGE) {
+				st = 0;
+				ph ^= 1;
+			}
 		}
 
+		const Item x = decode_item(wk, item);
+		if (tma_store) {
+			T *stage_out = reinterpret_cast<T *>(stages + size_t(NSTAGE) * STAGE_BYTES);
+			if (tid == 0)
+				tma_store_wait_read(); // the previous item's store has drained the staging tile
+			named_barrier(1, NCW * 32);
+			T *o = stage_out + ((ws * TN) * TT + wt * 32 + lane_t) * HG + lane_h;
+#pragma unroll
+			for (int j = 0; j < TN; j++)
+#pragma unroll
+				for (int i = 0; i < TM; i++)
+					o[(j * TT + LT * i) * HG] = acc[i][j] * scale;
+			fence_proxy_async_smem();
+			named_barrier(1, NCW * 32);
+			if (tid == 0) {
+				tma_store_4d(&omap, stage_out, x.h0, x.t0, x.s0, x.b);
+				tma_store_commit();
+			}
+			continue;
+		}
 		const int h = x.h0 + lane_h;
 		if (h < n_heads) {
 			T *ab = attn + size_t(x.b) * n_tok * n_tok * n_heads + h;
@@ -173,6 +196,8 @@ dense_fwd_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_cons
 			}
 		}
 	}
+	if (tma_store && tid == 0)
+		tma_store_wait_read(); // shared memory must outlive the last store's reads
 }
 
 template <typename T> CUtensorMapDataType tmap_dtype();
@@ -194,20 +219,33 @@ int launch(const T *q, const T *k, T *attn, int bs, int n_tok, int n_heads, int 
 	int *err = device_error_word();
 	if (!err)
 		return 1;
+	// output [bs][s][t][h] as a tensor for the TMA store; needs a 16-byte row pitch and base
+	CUtensorMap omap = qmap;
+	int tma_store = 0;
+	if ((size_t(n_heads) * sizeof(T)) % 16 == 0 && aligned(attn, 16)) {
+		const uint64_t odims[4] = {uint64_t(n_heads), uint64_t(n_tok), uint64_t(n_tok), uint64_t(bs)};
+		const uint64_t ostr[3] = {uint64_t(n_heads) * sizeof(T), uint64_t(n_tok) * n_heads * sizeof(T),
+					  uint64_t(n_tok) * n_tok * n_heads * sizeof(T)};
+		const uint32_t obox[4] = {HG, TT, TS, 1};
+		tma_store = encode_tmap_4d(&omap, tmap_dtype<T>(), attn, odims, ostr, obox, CU_TENSOR_MAP_SWIZZLE_NONE) ? 1 : 0;
+	}
 	Work wk;
 	wk.ntt = (n_tok + TT - 1) / TT;
 	wk.nst = (n_tok + TS - 1) / TS;
 	wk.nhg = (n_heads + HG - 1) / HG;
-	wk.total = (long long)bs * wk.nhg * wk.ntt * wk.nst;
+	const long long total = (long long)bs * wk.nhg * wk.ntt * wk.nst;
+	if (total > 0x7fffffffLL)
+		return L1ATTN_ERR_SHAPE;
+	wk.total = unsigned(total);
 	int dev = 0, sms = 0;
 	L1B_CUDA(cudaGetDevice(&dev));
 	L1B_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-	const long long grid = wk.total < sms ? wk.total : sms;
-	const size_t smem = size_t(NSTAGE) * STAGE_BYTES + 1024;
+	const unsigned grid = wk.total < unsigned(sms) ? wk.total : unsigned(sms);
+	const size_t smem = size_t(NSTAGE) * STAGE_BYTES + OUT_BYTES + 1024;
 	auto kern = dense_fwd_tma_kernel<T>;
 	L1B_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
 	const T scale = T(-1.0 / sqrt(double(width)));
-	kern<<<unsigned(grid), NTHREADS, smem, st>>>(qmap, kmap, attn, n_tok, n_heads, width, scale, wk, err);
+	kern<<<unsigned(grid), NTHREADS, smem, st>>>(qmap, kmap, omap, tma_store, attn, n_tok, n_heads, width, scale, wk, err);
 	L1B_LAUNCH_CHECK();
 	return L1ATTN_OK;
 }

@@ -66,6 +66,23 @@ __device__ __forceinline__ void tma_load_4d(void *dst, const CUtensorMap *map, u
 		     : "memory");
 }
 
+// 4-D tiled store shared -> global (bulk async-group completion).  Parts of the box outside the
+// tensor are clipped by the hardware; coordinates must be non-negative and c0 a multiple of 16 bytes.
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap *map, const void *src, int c0, int c1, int c2, int c3)
+{
+	asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+		     :
+		     : "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(src)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+		     : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// waits until every committed bulk store has finished READING its shared-memory source
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// makes generic-proxy shared-memory writes visible to the async proxy (before a bulk store reads them)
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+// barrier among the first `n` threads' warps only (id 1..15; 0 is __syncthreads)
+__device__ __forceinline__ void named_barrier(int id, int n) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(n) : "memory"); }
+
 // ---- host side -----------------------------------------------------------------------------
 
 // Encodes a 4-D tiled tensor map.  dims/box are innermost-first; strides_bytes has 3 entries (dims 1..3).
