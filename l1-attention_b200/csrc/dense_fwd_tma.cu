@@ -11,8 +11,8 @@
 //     work items, so the next item's tiles land while the current one is still being reduced;
 //   * warps 0..7 compute: lanes = 8 heads x 4 query rows, each thread keeps an 8 x 8 (query, key)
 //     register tile of its head, reads operands with conflict-free 16-byte shared loads (the
-//     swizzle spreads the 8 head-lanes over 8 bank groups) and spends 2 FP32 instructions per
-//     term (subtract; add with |.| as a source modifier).  Eight compute warps with ~160
+//     swizzle spreads the 8 head-lanes over 8 bank groups) and spends 1.5 issue slots per
+//     term (packed sub.f32x2 for two differences; scalar add with |.| as a source modifier).  Eight compute warps with ~160
 //     registers each (no spills) measured faster than sixteen with 128;
 //   * results leave through shared memory: the compute warps drop their scaled tiles into a
 //     [key][query][head] staging buffer (each warp store is one 128-byte row) and one thread issues
@@ -60,7 +60,7 @@ __device__ __forceinline__ Item decode_item(const Work &wk, unsigned r)
 	return x;
 }
 
-template <typename T>
+template <typename T> // instantiated for float only: the packed subtract below is fp32
 __global__ void __launch_bounds__(NTHREADS, 1)
 dense_fwd_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kmap,
 		     const __grid_constant__ CUtensorMap omap, int tma_store, T *__restrict__ attn, int n_tok, int n_heads, int width, T scale, Work wk, int *err)
@@ -130,23 +130,34 @@ dense_fwd_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_cons
 			// invalid and the error word says so) so that it still meets the others at the barriers
 			if (!dead && !mbar_wait(&full_bar[st], ph, err))
 				dead = true;
-			const V *S = reinterpret_cast<const V *>(stages + size_t(st) * STAGE_BYTES);
-			const V *qp = S + qoff, *kp = S + koff;
+			const ulonglong2 *S = reinterpret_cast<const ulonglong2 *>(stages + size_t(st) * STAGE_BYTES);
+			const ulonglong2 *qp = S + qoff, *kp = S + koff;
 #pragma unroll
 			for (int c = 0; c < CH; c++) {
 				const int pc = c ^ sw;
-				V kv[TN];
+				// Each 16-byte operand is two register pairs; the subtraction is the packed
+				// sub.f32x2 (one issue slot for two differences), the |.|-accumulation stays
+				// scalar because its abs is a free source modifier only there.
+				ulonglong2 kv[TN];
 #pragma unroll
 				for (int j = 0; j < TN; j++)
 					kv[j] = kp[j * HG * CH + pc];
 #pragma unroll
 				for (int i = 0; i < TM; i++) {
-					const V qv = qp[i * LT * HG * CH + pc];
+					const ulonglong2 qv = qp[i * LT * HG * CH + pc];
 #pragma unroll
-					for (int j = 0; j < TN; j++)
-#pragma unroll
-						for (int e = 0; e < VEC; e++)
-							acc[i][j] += absdiff(qv.v[e], kv[j].v[e]);
+					for (int j = 0; j < TN; j++) {
+						unsigned long long d0, d1;
+						float x0, x1, x2, x3;
+						asm("sub.f32x2 %0, %1, %2;" : "=l"(d0) : "l"(qv.x), "l"(kv[j].x));
+						asm("sub.f32x2 %0, %1, %2;" : "=l"(d1) : "l"(qv.y), "l"(kv[j].y));
+						asm("mov.b64 {%0, %1}, %2;" : "=f"(x0), "=f"(x1) : "l"(d0));
+						asm("mov.b64 {%0, %1}, %2;" : "=f"(x2), "=f"(x3) : "l"(d1));
+						acc[i][j] += fabsf(x0);
+						acc[i][j] += fabsf(x1);
+						acc[i][j] += fabsf(x2);
+						acc[i][j] += fabsf(x3);
+					}
 				}
 			}
 			__syncwarp();
