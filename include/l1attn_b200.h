@@ -41,6 +41,7 @@ extern "C" {
 #define L1ATTN_ERR_INDEX (-4)    /* coo holds a token / rank outside [0,n_tok) / [0,dst_mxlen) */
 #define L1ATTN_ERR_NOMEM (-5)    /* host-buffer entry point could not get device memory */
 #define L1ATTN_ERR_ALIGN (-6)    /* a floating tensor pointer is not aligned to its element size */
+#define L1ATTN_ERR_SCRATCH (-8)  /* problem needs more scratch than the library's built-in buffer holds */
 #define L1ATTN_ERR_TIMEOUT (-7)  /* a kernel gave up a bounded wait on an asynchronous copy (its output is invalid) */
 
 #define L1ATTN_F32 0
@@ -125,6 +126,29 @@ int l1attn_sparse_bwd(const void *dvo, const void *v, const void *vb, const void
 		      void *d_v, void *d_vb, void *d_q, void *d_k, void *scratch,
 		      int bs, int n_tok, int n_heads, int width, int v_width, int cl, int dst_mxlen,
 		      int use_softmax, int bidi, int dtype, void *stream);
+
+/*
+ * l1attn_sparse_bwd for callers that cannot allocate device memory at the point where they run the
+ * backward (a plugin that only receives device pointers from its host runtime, or code in a region
+ * where cudaMalloc is forbidden or would stall the device).  Same arguments without `scratch`: the
+ * d(logit) buffer is a fixed 32 MiB array inside the library's device image
+ * (l1attn_sparse_bwd_static_capacity() bytes), so the call allocates nothing, neither with the CUDA
+ * runtime nor through any library.  It fails with L1ATTN_ERR_SCRATCH, before launching anything, when
+ * l1attn_sparse_bwd_scratch_bytes(bs, n_tok, n_heads, dst_mxlen, dtype) exceeds that capacity.
+ * The first call on each device looks up the array's device address (a CUDA runtime query, no
+ * allocation); make that first call outside any stream capture.  All calls on a device share the one
+ * array: calls whose kernels can overlap on the GPU (different streams) must not be issued
+ * concurrently; on a single stream they are ordered and safe.  The array keeps whatever the last call
+ * left; the kernels overwrite every entry they later read, so nothing needs clearing.
+ * No counterpart in the reference, whose backward allocates its two scratch tensors with torch
+ * on every call (cuda/l1attn_sparse_cuda_kernel.cu:447-531).
+ */
+size_t l1attn_sparse_bwd_static_capacity(void);
+int l1attn_sparse_bwd_static(const void *dvo, const void *v, const void *vb, const void *q, const void *k,
+			     const void *index, const void *attn,
+			     void *d_v, void *d_vb, void *d_q, void *d_k,
+			     int bs, int n_tok, int n_heads, int width, int v_width, int cl, int dst_mxlen,
+			     int use_softmax, int bidi, int dtype, void *stream);
 
 /* ------------------------------------------------------------------ expandCoo ----------- */
 

@@ -98,6 +98,7 @@ extern "C" const char *l1attn_strerror(int code)
 	case L1ATTN_ERR_INDEX: return "coo row outside [0,n_tok) x [0,n_tok) x [0,dst_mxlen)";
 	case L1ATTN_ERR_NOMEM: return "out of device memory";
 	case L1ATTN_ERR_ALIGN: return "tensor pointer not aligned to its element size";
+	case L1ATTN_ERR_SCRATCH: return "the problem needs more scratch memory than the library's built-in static buffer holds";
 	case L1ATTN_ERR_TIMEOUT: return "a kernel gave up a bounded wait on an asynchronous copy";
 	default: return "unknown l1attn error code";
 	}

@@ -9,6 +9,7 @@
 // bit-reproducible.  Within a warp LPH lanes share a head and split its width; a head's dot
 // products / L1 sums are finished with xor-shuffles.
 #include <initializer_list>
+#include <mutex>
 #include "common.cuh"
 
 namespace l1b {
@@ -478,4 +479,62 @@ extern "C" int l1attn_sparse_bwd(const void *dvo, const void *v, const void *vb,
 	return bwd_t<double, 1>(a, (const double *)dvo, (const double *)v, (const double *)vb, (const double *)q,
 				(const double *)k, (const double *)attn, (double *)d_v, (double *)d_vb, (double *)d_q,
 				(double *)d_k, (double *)scratch, st);
+}
+
+// ------------------------------------------------------------------------------------------------
+// Sparse backward for callers that must not allocate.
+//
+// Some hosts of this library cannot call cudaMalloc where they run the backward: a plugin that is
+// handed device pointers by an embedding runtime and has no allocator of its own, or code inside a
+// region where allocation is forbidden or would synchronise the device.  For them the per-slot
+// d(logit) buffer that l1attn_sparse_bwd takes as `scratch` lives here, in a fixed array in the
+// library's device image.  Every GPU that loads the library carries these 32 MiB until the process
+// exits, and every call on a device shares them, so two such calls that overlap on the GPU (different
+// streams) race; calls on one stream are safe.  Nothing in the array has to start at zero: the dst
+// pass writes the entry of every real edge slot before the src pass reads it, and entries of empty
+// slots are never read, so stale contents of an earlier call are harmless.
+constexpr size_t STATIC_SCRATCH_BYTES = size_t(32) << 20;
+static __device__ __align__(256) unsigned char g_sparse_bwd_scratch[STATIC_SCRATCH_BYTES];
+
+namespace {
+constexpr int MAX_DEVICES = 64;
+void *g_scratch_addr[MAX_DEVICES]; // device address of the array, per device, filled on first use
+std::mutex g_scratch_mu;
+
+// In host code the array's name is only a handle; the address a kernel can use comes from
+// cudaGetSymbolAddress, asked for once per device with that device current.
+int static_scratch_for_current_device(void **out)
+{
+	int dev = 0;
+	L1B_CUDA(cudaGetDevice(&dev));
+	if (dev < 0 || dev >= MAX_DEVICES)
+		return L1ATTN_ERR_ARG;
+	std::lock_guard<std::mutex> lock(g_scratch_mu);
+	if (!g_scratch_addr[dev]) {
+		void *p = nullptr;
+		L1B_CUDA(cudaGetSymbolAddress(&p, g_sparse_bwd_scratch));
+		g_scratch_addr[dev] = p;
+	}
+	*out = g_scratch_addr[dev];
+	return L1ATTN_OK;
+}
+} // namespace
+
+extern "C" size_t l1attn_sparse_bwd_static_capacity(void) { return STATIC_SCRATCH_BYTES; }
+
+extern "C" int l1attn_sparse_bwd_static(const void *dvo, const void *v, const void *vb, const void *q, const void *k,
+					 const void *index, const void *attn, void *d_v, void *d_vb, void *d_q,
+					 void *d_k, int bs, int n_tok, int n_heads, int width, int v_width, int cl,
+					 int dst_mxlen, int use_softmax, int bidi, int dtype, void *stream)
+{
+	int rc = check_sparse(bs, n_tok, n_heads, width, v_width, cl, dst_mxlen, dtype);
+	if (rc)
+		return rc;
+	if (l1attn_sparse_bwd_scratch_bytes(bs, n_tok, n_heads, dst_mxlen, dtype) > STATIC_SCRATCH_BYTES)
+		return L1ATTN_ERR_SCRATCH;
+	void *scratch = nullptr;
+	if ((rc = static_scratch_for_current_device(&scratch)))
+		return rc;
+	return l1attn_sparse_bwd(dvo, v, vb, q, k, index, attn, d_v, d_vb, d_q, d_k, scratch, bs, n_tok, n_heads, width,
+				 v_width, cl, dst_mxlen, use_softmax, bidi, dtype, stream);
 }

@@ -32,6 +32,8 @@ SIGNATURES = {
     "l1attn_sparse_fwd": (_i, [_vp] * 7 + [_i] * 10 + [_vp]),
     "l1attn_sparse_bwd_scratch_bytes": (_sz, [_i] * 5),
     "l1attn_sparse_bwd": (_i, [_vp] * 12 + [_i] * 10 + [_vp]),
+    "l1attn_sparse_bwd_static_capacity": (_sz, []),
+    "l1attn_sparse_bwd_static": (_i, [_vp] * 11 + [_i] * 10 + [_vp]),
     "l1attn_expand_coo_scratch_bytes": (_sz, [_ll]),
     "l1attn_expand_coo": (_i, [_vp, _i, _vp, _vp, _ll, _ll, _vp, _vp]),
     "l1attn_i64_minmax": (_i, [_vp, _ll, _vp, _vp]),
@@ -239,4 +241,22 @@ def sparse_bwd(dvo, v, q, k, index, attn, use_softmax=True, vb=None, out=None, s
                                    _dp(dvb), _dp(dq), _dp(dk), _dp(scratch), bs, n, h, w, wv, index.cl,
                                    index.dst_mxlen, int(bool(use_softmax)), int(vb is not None), _tdt(q), _stream()),
            "l1attn_sparse_bwd")
+    return (dv, dq, dk) if vb is None else (dv, dvb, dq, dk)
+
+
+def sparse_bwd_static(dvo, v, q, k, index, attn, use_softmax=True, vb=None, out=None):
+    """As sparse_bwd, through l1attn_sparse_bwd_static: the d(logit) scratch is the library's own
+    fixed device array, so neither this helper nor the library allocates scratch for the call
+    (the gradient tensors are allocated here only when `out` is not given)."""
+    import torch
+    bs, n, h, w = q.shape
+    wv = v.shape[3]
+    if out is None:
+        out = (torch.empty_like(v), torch.empty_like(v) if vb is not None else None,
+               torch.empty_like(q), torch.empty_like(k))
+    dv, dvb, dq, dk = out
+    _check(lib().l1attn_sparse_bwd_static(_dp(dvo), _dp(v), _dp(vb), _dp(q), _dp(k), _dp(index.buf), _dp(attn),
+                                          _dp(dv), _dp(dvb), _dp(dq), _dp(dk), bs, n, h, w, wv, index.cl,
+                                          index.dst_mxlen, int(bool(use_softmax)), int(vb is not None), _tdt(q),
+                                          _stream()), "l1attn_sparse_bwd_static")
     return (dv, dq, dk) if vb is None else (dv, dvb, dq, dk)
