@@ -75,10 +75,15 @@ int l1attn_dense_fwd(const void *q, const void *k, void *attn,
  * d_q[b][t][h][w] =  scale * sum_s sign(q[b][t][h][w]-k[b][s][h][w]) * d_attn[b][s][t][h]
  * d_k[b][s][h][w] = -scale * sum_t sign(q[b][t][h][w]-k[b][s][h][w]) * d_attn[b][s][t][h]
  * with scale = -1/sqrt(width) and sign(0) = 0.  Deterministic (no atomics).
+ * `scratch`: device buffer of l1attn_dense_bwd_scratch_bytes() bytes (a few KB: one flag per
+ * tile, written by a detector kernel that finds exact ties q == k so that tie-free tiles can take
+ * a shorter inner loop), or NULL, in which case every tile takes the exact loop (same results,
+ * roughly twice the time in fp32).
  * Replaces l1attn_cuda_drv.backward (cuda/l1attn_cuda_drv.cpp:67-104) and
  * l1attn_cuda_backward{,32,64} (cuda/l1attn_cuda_kernel.cu:559-685).
  */
-int l1attn_dense_bwd(const void *d_attn, const void *q, const void *k, void *d_q, void *d_k,
+size_t l1attn_dense_bwd_scratch_bytes(int bs, int n_tok, int n_heads, int width, int dtype);
+int l1attn_dense_bwd(const void *d_attn, const void *q, const void *k, void *d_q, void *d_k, void *scratch,
 		     int bs, int n_tok, int n_heads, int width, int dtype, void *stream);
 
 /* ------------------------------------------------------------------ sparse -------------- */

@@ -116,14 +116,19 @@ extern "C" int l1attn_dense_fwd(const void *q, const void *k, void *attn, int bs
 	return dense_fwd_launch(q, k, attn, bs, n_tok, n_heads, width, dtype, static_cast<cudaStream_t>(stream));
 }
 
-extern "C" int l1attn_dense_bwd(const void *d_attn, const void *q, const void *k, void *d_q, void *d_k, int bs,
-				 int n_tok, int n_heads, int width, int dtype, void *stream)
+extern "C" size_t l1attn_dense_bwd_scratch_bytes(int bs, int n_tok, int n_heads, int width, int dtype)
+{
+	return dense_bwd_scratch_bytes(bs, n_tok, n_heads, width, dtype);
+}
+
+extern "C" int l1attn_dense_bwd(const void *d_attn, const void *q, const void *k, void *d_q, void *d_k, void *scratch,
+				 int bs, int n_tok, int n_heads, int width, int dtype, void *stream)
 {
 	const void *ptrs[] = {d_attn, q, k, d_q, d_k};
 	int rc = check_dense(ptrs, 5, bs, n_tok, n_heads, width, dtype);
 	if (rc)
 		return rc;
-	return dense_bwd_launch(d_attn, q, k, d_q, d_k, bs, n_tok, n_heads, width, dtype,
+	return dense_bwd_launch(d_attn, q, k, d_q, d_k, scratch, bs, n_tok, n_heads, width, dtype,
 				static_cast<cudaStream_t>(stream));
 }
 
@@ -174,14 +179,15 @@ extern "C" int l1attn_dense_bwd_host(const void *d_attn, const void *q, const vo
 	Arena *ar = arena_for_current(&rc);
 	if (!ar)
 		return rc;
-	if ((rc = arena_reserve(ar, 4 * pad256(nqk) + pad256(na))))
+	const size_t nsc = dense_bwd_scratch_bytes(bs, n_tok, n_heads, width, dtype);
+	if ((rc = arena_reserve(ar, 4 * pad256(nqk) + pad256(na) + pad256(nsc))))
 		return rc;
 	void *dq = arena_take(ar, nqk), *dk = arena_take(ar, nqk), *dg = arena_take(ar, na);
-	void *ddq = arena_take(ar, nqk), *ddk = arena_take(ar, nqk);
+	void *ddq = arena_take(ar, nqk), *ddk = arena_take(ar, nqk), *dsc = arena_take(ar, nsc);
 	H2D(dq, q, nqk);
 	H2D(dk, k, nqk);
 	H2D(dg, d_attn, na);
-	if ((rc = dense_bwd_launch(dg, dq, dk, ddq, ddk, bs, n_tok, n_heads, width, dtype, 0)))
+	if ((rc = dense_bwd_launch(dg, dq, dk, ddq, ddk, dsc, bs, n_tok, n_heads, width, dtype, 0)))
 		return rc;
 	D2H(d_q, ddq, nqk);
 	D2H(d_k, ddk, nqk);

@@ -69,8 +69,15 @@ int dense_fwd_launch(const void *q, const void *k, void *attn, int bs, int n_tok
 // fast paths: return 1 when they do not apply to the given shape / alignment / device
 int dense_fwd_tma_launch(const void *q, const void *k, void *attn, int bs, int n_tok, int n_heads, int width,
 			 int dtype, cudaStream_t st);
-int dense_bwd_launch(const void *d_attn, const void *q, const void *k, void *d_q, void *d_k, int bs, int n_tok,
-		     int n_heads, int width, int dtype, cudaStream_t st);
+int dense_bwd_tma_launch(const void *d_attn, const void *q, const void *k, void *d_q, void *d_k, int bs, int n_tok,
+			 int n_heads, int width, int dtype, const unsigned char *exact_flags, cudaStream_t st);
+size_t dense_bwd_tma_flag_count(int bs, int n_tok, int n_heads, int width);
+int dense_ties_launch(const float *q, const float *k, unsigned char *flags, int bs, int n_tok, int n_heads, int width,
+		      cudaStream_t st);
+// scratch: dense_bwd_scratch_bytes() bytes of device memory, or nullptr (then every tile runs the exact loop)
+int dense_bwd_launch(const void *d_attn, const void *q, const void *k, void *d_q, void *d_k, void *scratch, int bs,
+		     int n_tok, int n_heads, int width, int dtype, cudaStream_t st);
+size_t dense_bwd_scratch_bytes(int bs, int n_tok, int n_heads, int width, int dtype);
 
 // Layout of the sparse edge index (all int32, each array padded to 16 bytes):
 //   slot_src [n_tok*dst_mxlen]  src token of slot (dst, r), or -1

@@ -8,6 +8,7 @@
 // 8 heads and a slice of the width, keeps its `a` values and accumulators in registers and
 // streams y in tiles through shared memory.  Every output element is produced by exactly one
 // thread in a fixed order: no atomics, bit-reproducible.
+#include <cstdlib>
 #include "common.cuh"
 
 namespace l1b {
@@ -171,11 +172,35 @@ int launch(const T *g, const T *q, const T *k, T *d_q, T *d_k, int bs, int n_tok
 
 } // namespace
 
-int dense_bwd_launch(const void *d_attn, const void *q, const void *k, void *d_q, void *d_k, int bs, int n_tok,
-		     int n_heads, int width, int dtype, cudaStream_t st)
+size_t dense_bwd_scratch_bytes(int bs, int n_tok, int n_heads, int width, int dtype)
+{
+	if (dtype != L1ATTN_F32 || bs <= 0 || n_tok <= 0 || n_heads <= 0 || width <= 0)
+		return 16;
+	return ((dense_bwd_tma_flag_count(bs, n_tok, n_heads, width) + 255) / 256) * 256; // tie flags of the fast path
+}
+
+int dense_bwd_launch(const void *d_attn, const void *q, const void *k, void *d_q, void *d_k, void *scratch, int bs,
+		     int n_tok, int n_heads, int width, int dtype, cudaStream_t st)
 {
 	if (bs == 0 || n_tok == 0 || n_heads == 0 || width == 0)
 		return L1ATTN_OK;
+	static const bool no_tma = getenv("L1ATTN_NO_TMA") != nullptr; // debugging aid: force the generic kernel
+	if (!no_tma) {
+		// per-tile tie flags let tie-free tiles use the two-instruction form; without scratch
+		// (or when the detector does not apply) every tile runs the exact loop
+		unsigned char *flags = nullptr;
+		if (scratch && dtype == L1ATTN_F32 && width % 4 == 0 && n_heads % 4 == 0) {
+			const int trc = dense_ties_launch((const float *)q, (const float *)k, (unsigned char *)scratch, bs, n_tok,
+							  n_heads, width, st);
+			if (trc < 0)
+				return trc;
+			if (trc == 0)
+				flags = (unsigned char *)scratch;
+		}
+		const int rc = dense_bwd_tma_launch(d_attn, q, k, d_q, d_k, bs, n_tok, n_heads, width, dtype, flags, st);
+		if (rc <= 0)
+			return rc;
+	}
 	if (dtype == L1ATTN_F32)
 		return launch<float, 8, 4, 2>((const float *)d_attn, (const float *)q, (const float *)k, (float *)d_q,
 					      (float *)d_k, bs, n_tok, n_heads, width, st);

@@ -1,0 +1,355 @@
+// Dense L1 scores, backward -- the B200 fast path (fp32).
+//
+//   d_q[b][t][h][w] =  scale * sum_s sign(q[b][t][h][w] - k[b][s][h][w]) * g[b][s][t][h]
+//   d_k[b][s][h][w] = -scale * sum_t sign(q[b][t][h][w] - k[b][s][h][w]) * g[b][s][t][h]     sign(0) = 0
+//
+// Both are  out[x][h][w] = scale * sum_y sign(a[x][h][w] - b[y][h][w]) * G(x, y, h)
+// (pass 0: a=q, b=k, x=t, y=s;  pass 1: a=k, b=q, x=s, y=t;  G(x,y,h) = g[s][t][h] either way).
+// Each output element is owned by one thread and summed in a fixed order: no atomics, no scratch
+// partials, bit-reproducible.  The price is that every term is visited twice (once per pass); the
+// gain is that a visit is two instructions.
+//
+// Two instructions per term.  With no ties (a != b) in a tile,
+//     sum_y sign(a-b) G = 2 * sum_y [a > b] G  -  sum_y G,
+// so the inner loop is one compare (FSETP) and one predicated add per term; the row sums
+// sum_y G(x,y,h) are a by-product (4 extra adds per 32 terms).  A (work item, y tile) pair may use
+// this form unless a detector kernel (dense_ties.cu) has found a token row in the x tile AND one in
+// the y tile that take part in a tie a == b (same batch, head, width index); such pairs run the
+// exact loop (subtract, sign transfer, tie predicate, add) on halved G, so that one accumulator
+// serves both forms: out = scale * (2 acc - R), R summed over the compare-form tiles only.
+// Exact ties between random floats occur ~1.5e-8 per term (a few hundred per call at 16x1024x16x64),
+// zero-padded tokens tie everywhere; both cases stay exact and cost the exact loop only where they occur.
+//
+// Structure: one persistent launch per pass, one CTA per SM, work item = (batch, 8 heads, 32 x-rows,
+// all 64 width columns of a 64-wide slice).  One thread streams y in tiles of 16 through a 4-stage
+// ring of TMA tensor loads (no multicast): the b rows as two [y][head][32 w] boxes with the 128-byte
+// swizzle, and the G tile as a [.][.][8 heads] box of the heads-innermost gradient tensor -- 32-byte
+// runs, whole sectors, no transposed copy of d_attn (the reference makes one).  16 warps:
+// lanes = 8 heads x 4 width chunks, a thread owns 4 x-rows x 8 width columns of one head (32 `a`
+// values and 32 accumulators in registers) and per y reads 2 x 16 bytes of b and 4 G scalars.
+// (8 warps with 8 x 8 tiles measured half the speed: with two warps per scheduler the
+// compare -> predicated-add latency was exposed, "wait" stalls of ~5 cycles per instruction.)
+// All mbarrier waits are bounded (tma.cuh).
+#include "common.cuh"
+#include "tma.cuh"
+#include "dense_bwd_tiles.h"
+
+namespace l1b {
+namespace {
+
+constexpr int HG = BWD_HG; // heads per work item = lanes along heads (8)
+constexpr int TX = BWD_TX; // x rows per work item (32)
+constexpr int TY = BWD_TY; // y rows per stage (16)
+constexpr int WS = BWD_WS; // width slice per work item (64 = two 32-wide halves)
+constexpr int NCW = 16;  // warps: 8 x-groups of XR rows x 2 halves of the chunk range
+constexpr int XR = 4;    // x rows per thread
+constexpr int NSTAGE = 4;
+constexpr int B_BYTES = TY * HG * 32 * 4;  // one 32-wide half of the b tile: 16384
+constexpr int G_BYTES = TY * TX * HG * 4;  // 16384
+constexpr int STAGE_BYTES = 2 * B_BYTES + G_BYTES; // 49152
+constexpr int NTHREADS = NCW * 32; // 512 threads x 128 registers; 4 warps per scheduler hide the compare->add latency
+
+struct BwdWork {
+	unsigned nxt, nws, nhg, bs, per_pass, total;
+	int ny; // y tiles per item
+};
+struct BwdItem {
+	int b, h0, w0, x0;
+};
+__device__ __forceinline__ BwdItem decode(const BwdWork &wk, unsigned r)
+{
+	BwdItem it;
+	it.x0 = int(r % wk.nxt) * TX;
+	r /= wk.nxt;
+	it.w0 = int(r % wk.nws) * WS;
+	r /= wk.nws;
+	it.h0 = int(r % wk.nhg) * HG;
+	it.b = int(r / wk.nhg);
+	return it;
+}
+
+// one stage (TY rows of y) of the inner loop for the calling thread
+template <int PASS, bool EXACT>
+__device__ __forceinline__ void tile_loop(const unsigned char *stage, int h, int c, int wx, int wp, const float (&a)[XR][8],
+					  float (&acc)[XR][8], float (&rs)[XR])
+{
+	const float4 *B0 = reinterpret_cast<const float4 *>(stage);
+	const float4 *B1 = reinterpret_cast<const float4 *>(stage + B_BYTES);
+	const float *G = reinterpret_cast<const float *>(stage + 2 * B_BYTES);
+	// G tile layout: pass 0 [y][x][h], pass 1 [x][y][h]
+	const float *gp = G + (PASS == 0 ? (wx * XR) * HG : (wx * XR) * TY * HG) + h;
+	constexpr int GI = PASS == 0 ? HG : TY * HG;  // stride between this thread's x rows
+	constexpr int GY = PASS == 0 ? TX * HG : HG;  // stride between y rows
+	const int boff = h * 8 + (c ^ h); // 128-byte swizzle: chunk ^= (row & 7), row = y*8 + h
+#pragma unroll 4
+	for (int y = 0; y < TY; y++) {
+		const float4 b0 = B0[y * 64 + boff], b1 = B1[y * 64 + boff];
+		const float bv[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+		float g[XR];
+#pragma unroll
+		for (int i = 0; i < XR; i++)
+			g[i] = gp[y * GY + i * GI];
+		if (!EXACT) {
+#pragma unroll
+			for (int i = 0; i < XR; i++)
+				rs[i] += g[i];
+		}
+		if (EXACT) {
+#pragma unroll
+			for (int i = 0; i < XR; i++)
+#pragma unroll
+				for (int e = 0; e < 8; e++) // halves: the epilogue doubles every accumulator (exact in binary fp)
+					acc[i][e] += sign_apply(a[i][e] - bv[e], 0.5f * g[i]);
+		} else {
+			// compare + predicated add, spelled in PTX four terms at a time (four compares, then four
+			// adds): left to the compiler the term becomes compare + add + select, two instructions on
+			// the half-rate ALU pipe, and single compare/add pairs were scheduled back to back with
+			// the compare latency exposed
+#pragma unroll
+			for (int i = 0; i < XR; i++)
+#pragma unroll
+				for (int e = 0; e < 8; e += 4)
+					asm("{\n\t.reg .pred p0, p1, p2, p3;\n\t"
+					    "setp.gt.f32 p0, %4, %8;\n\tsetp.gt.f32 p1, %5, %9;\n\t"
+					    "setp.gt.f32 p2, %6, %10;\n\tsetp.gt.f32 p3, %7, %11;\n\t"
+					    "@p0 add.f32 %0, %0, %12;\n\t@p1 add.f32 %1, %1, %12;\n\t"
+					    "@p2 add.f32 %2, %2, %12;\n\t@p3 add.f32 %3, %3, %12;\n\t}"
+					    : "+f"(acc[i][e]), "+f"(acc[i][e + 1]), "+f"(acc[i][e + 2]), "+f"(acc[i][e + 3])
+					    : "f"(a[i][e]), "f"(a[i][e + 1]), "f"(a[i][e + 2]), "f"(a[i][e + 3]), "f"(bv[e]),
+					      "f"(bv[e + 1]), "f"(bv[e + 2]), "f"(bv[e + 3]), "f"(g[i]));
+		}
+	}
+}
+
+// The hot loop needs the predicate registers (only seven exist) for its compare -> add pairs.  Any
+// boolean that stays live across that loop (bounds tests reused by the epilogue, "is thread 0", "has a
+// wait timed out") takes one away, and with one or two left the pairs run strictly one after the
+// other.  Passing the integers such tests are made from through this no-op makes the compiler
+// recompute the test where it is used instead of keeping its result in a predicate.
+__device__ __forceinline__ int opaque(int x)
+{
+	asm volatile("" : "+r"(x));
+	return x;
+}
+
+// Feeding cursor of the TMA ring; lives in shared memory so that it costs the compute threads no
+// registers (only thread 0 touches it).
+struct Feeder {
+	unsigned item;
+	int yt, st;
+	uint32_t ph;
+	int dead;
+};
+
+// PASS 0: d_q (a = q, b = k, x = t, y = s).  PASS 1: d_k (a = k, b = q, x = s, y = t).
+template <int PASS>
+__global__ void __launch_bounds__(NTHREADS, 1)
+dense_bwd_tma_kernel(const __grid_constant__ CUtensorMap bmap, const __grid_constant__ CUtensorMap gmap,
+		     const float *__restrict__ av_base, float *__restrict__ out_base,
+		     const unsigned char *__restrict__ flags, BwdFlagLayout fl, int n_tok, int n_heads, int width,
+		     float scale, BwdWork wk, int *err)
+{
+	extern __shared__ __align__(1024) unsigned char smem_raw[];
+	// 1024-byte alignment by OFFSET into the shared array: a pointer rebuilt from an integer loses its
+	// address space and every access through it becomes a generic load, which measured ~2x slower here
+	unsigned char *stages = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+	__shared__ __align__(8) uint64_t full_bar[NSTAGE], empty_bar[NSTAGE];
+	__shared__ Feeder fd;
+
+	const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+	if (tid == 0) {
+		for (int s = 0; s < NSTAGE; s++) {
+			mbar_init(&full_bar[s], 1);
+			mbar_init(&empty_bar[s], NCW);
+		}
+		mbar_fence_init();
+		fd.item = blockIdx.x;
+		fd.yt = 0;
+		fd.st = 0;
+		fd.ph = 1;
+		fd.dead = 0;
+	}
+	__syncthreads();
+
+	// Thread 0 keeps the ring NSTAGE-2 tiles ahead of the math: before each y tile it refills the
+	// stage that every warp released two tiles ago, so it never waits for a straggler.
+	auto issue_one = [&]() {
+		if (fd.item >= wk.per_pass || fd.dead)
+			return;
+		const int st = fd.st;
+		if (!mbar_wait(&empty_bar[st], fd.ph, err)) {
+			fd.dead = 1;
+			return;
+		}
+		const BwdItem x = decode(wk, fd.item);
+		unsigned char *dst = stages + size_t(st) * STAGE_BYTES;
+		const int y0 = fd.yt * TY;
+		mbar_expect_tx(&full_bar[st], STAGE_BYTES);
+		tma_load_4d(dst, &bmap, &full_bar[st], x.w0, x.h0, y0, x.b);
+		tma_load_4d(dst + B_BYTES, &bmap, &full_bar[st], x.w0 + 32, x.h0, y0, x.b);
+		if (PASS == 0) // box {8 h, TX t, TY s}
+			tma_load_4d(dst + 2 * B_BYTES, &gmap, &full_bar[st], x.h0, x.x0, y0, x.b);
+		else // box {8 h, TY t, TX s}
+			tma_load_4d(dst + 2 * B_BYTES, &gmap, &full_bar[st], x.h0, y0, x.x0, x.b);
+		if (st + 1 == NSTAGE) {
+			fd.st = 0;
+			fd.ph ^= 1;
+		} else {
+			fd.st = st + 1;
+		}
+		if (++fd.yt == wk.ny) {
+			fd.yt = 0;
+			fd.item += gridDim.x;
+		}
+	};
+	if (tid == 0)
+		for (int i = 0; i < NSTAGE - 2; i++)
+			issue_one();
+
+	const int lh = lane & 7, lw = lane >> 3;
+	const int wx = warp & 7, wp = warp >> 3;
+	const int c = lw + 4 * wp; // 16-byte chunk (0..7) of each 32-wide half
+	int st = 0;
+	uint32_t ph = 0;
+	int dead = 0;
+	for (unsigned item = blockIdx.x; item < wk.per_pass; item += gridDim.x) {
+		float a[XR][8], acc[XR][8], rs[XR] = {0.f, 0.f, 0.f, 0.f};
+		{
+			const BwdItem x = decode(wk, item);
+			const int h = x.h0 + lh;
+			const size_t row = size_t(n_heads) * width;
+			const float *av = av_base + size_t(x.b) * n_tok * row + size_t(h) * width;
+#pragma unroll
+			for (int i = 0; i < XR; i++) {
+				const int xr = x.x0 + wx * XR + i;
+#pragma unroll
+				for (int half = 0; half < 2; half++) {
+					const int w = x.w0 + half * 32 + c * 4;
+					float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+					if (xr < n_tok && h < n_heads && w < width)
+						v = *reinterpret_cast<const float4 *>(av + size_t(xr) * row + w);
+					a[i][half * 4 + 0] = v.x;
+					a[i][half * 4 + 1] = v.y;
+					a[i][half * 4 + 2] = v.z;
+					a[i][half * 4 + 3] = v.w;
+				}
+#pragma unroll
+				for (int e = 0; e < 8; e++)
+					acc[i][e] = 0.f;
+			}
+		}
+		// exact loop where a tile with a tying x row meets a tile with a tying y row (or always, without flags)
+		const int xflag = flags == nullptr ? 1 : int(flags[fl.xoff(PASS) + item]);
+		const unsigned char *yflags = flags == nullptr ? nullptr : flags + fl.yoff(PASS) + size_t(item / wk.nxt) * fl.ny;
+
+		for (int yt = 0; yt < wk.ny; yt++) {
+			if (opaque(tid) == 0)
+				issue_one();
+			__syncwarp();
+			if (opaque(dead) == 0 && !mbar_wait(&full_bar[st], ph, err))
+				dead = 1; // keep walking without waiting so the warps stay in step
+			const unsigned char *stage = stages + size_t(st) * STAGE_BYTES;
+			const bool exact = opaque(xflag) != 0 && (yflags == nullptr || yflags[yt] != 0); // yflags is read only for flagged x tiles
+			if (exact)
+				tile_loop<PASS, true>(stage, lh, c, wx, wp, a, acc, rs);
+			else
+				tile_loop<PASS, false>(stage, lh, c, wx, wp, a, acc, rs);
+			__syncwarp();
+			if (opaque(lane) == 0)
+				mbar_arrive(&empty_bar[st]);
+			if (++st == NSTAGE) {
+				st = 0;
+				ph ^= 1;
+			}
+		}
+
+		const BwdItem x = decode(wk, unsigned(opaque(int(item))));
+		const int h = x.h0 + opaque(lh);
+		const size_t row = size_t(n_heads) * width;
+		float *ov = out_base + size_t(x.b) * n_tok * row + size_t(h) * width;
+#pragma unroll
+		for (int i = 0; i < XR; i++) {
+			const int xr = x.x0 + wx * XR + i;
+			const float r = rs[i]; // sum of G(x, y, h) over the y tiles that took the compare form
+#pragma unroll
+			for (int half = 0; half < 2; half++) {
+				const int w = x.w0 + half * 32 + c * 4;
+				if (xr < n_tok && h < n_heads && w < width) {
+					float4 o;
+					float *op = reinterpret_cast<float *>(&o);
+#pragma unroll
+					for (int e = 0; e < 4; e++)
+						op[e] = fmaf(2.f, acc[i][half * 4 + e], -r) * scale;
+					*reinterpret_cast<float4 *>(ov + size_t(xr) * row + w) = o;
+				}
+			}
+		}
+	}
+}
+
+} // namespace
+
+// Returns L1ATTN_OK, a negative error, or 1 when this path does not apply.
+// flags: device tie flags laid out by bwd_flag_layout() and filled by dense_ties_launch(), or nullptr = all exact.
+int dense_bwd_tma_launch(const void *d_attn, const void *q, const void *k, void *d_q, void *d_k, int bs, int n_tok,
+			 int n_heads, int width, int dtype, const unsigned char *flags, cudaStream_t st)
+{
+	if (dtype != L1ATTN_F32)
+		return 1;
+	if (width % 4 != 0 || n_heads % 4 != 0)
+		return 1; // row pitches of q/k and of d_attn must be multiples of 16 bytes for the tensor maps
+	for (const void *p : {d_attn, q, k, (const void *)d_q, (const void *)d_k})
+		if (!aligned(p, 16))
+			return 1;
+	const uint64_t qdims[4] = {uint64_t(width), uint64_t(n_heads), uint64_t(n_tok), uint64_t(bs)};
+	const uint64_t qstr[3] = {uint64_t(width) * 4, uint64_t(n_heads) * width * 4, uint64_t(n_tok) * n_heads * width * 4};
+	const uint32_t bbox[4] = {32, HG, TY, 1};
+	const uint64_t gdims[4] = {uint64_t(n_heads), uint64_t(n_tok), uint64_t(n_tok), uint64_t(bs)};
+	const uint64_t gstr[3] = {uint64_t(n_heads) * 4, uint64_t(n_tok) * n_heads * 4, uint64_t(n_tok) * n_tok * n_heads * 4};
+	const uint32_t gbox0[4] = {HG, TX, TY, 1}, gbox1[4] = {HG, TY, TX, 1};
+	CUtensorMap qmap, kmap, gmap0, gmap1;
+	if (!encode_tmap_4d(&qmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, q, qdims, qstr, bbox, CU_TENSOR_MAP_SWIZZLE_128B) ||
+	    !encode_tmap_4d(&kmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, k, qdims, qstr, bbox, CU_TENSOR_MAP_SWIZZLE_128B) ||
+	    !encode_tmap_4d(&gmap0, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, d_attn, gdims, gstr, gbox0, CU_TENSOR_MAP_SWIZZLE_NONE) ||
+	    !encode_tmap_4d(&gmap1, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, d_attn, gdims, gstr, gbox1, CU_TENSOR_MAP_SWIZZLE_NONE))
+		return 1;
+	int *err = device_error_word();
+	if (!err)
+		return 1;
+	BwdWork wk;
+	wk.nxt = (n_tok + TX - 1) / TX;
+	wk.nws = (width + WS - 1) / WS;
+	wk.nhg = (n_heads + HG - 1) / HG;
+	wk.bs = bs;
+	const long long per_pass = (long long)bs * wk.nhg * wk.nws * wk.nxt;
+	if (2 * per_pass > 0x7fffffffLL)
+		return L1ATTN_ERR_SHAPE;
+	wk.per_pass = unsigned(per_pass);
+	wk.total = unsigned(2 * per_pass);
+	wk.ny = (n_tok + TY - 1) / TY;
+	int dev = 0, sms = 0;
+	L1B_CUDA(cudaGetDevice(&dev));
+	L1B_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+	const unsigned grid = wk.per_pass < unsigned(sms) ? wk.per_pass : unsigned(sms);
+	const size_t smem = size_t(NSTAGE) * STAGE_BYTES + 1024;
+	L1B_CUDA(cudaFuncSetAttribute(dense_bwd_tma_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+	L1B_CUDA(cudaFuncSetAttribute(dense_bwd_tma_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+	const float scale = float(-1.0 / sqrt(double(width)));
+	const BwdFlagLayout fl = bwd_flag_layout(bs, n_tok, n_heads, width);
+	// pass 0: d_q from (a = q, b = k);  pass 1: d_k from (a = k, b = q); one launch each, same stream
+	dense_bwd_tma_kernel<0><<<grid, NTHREADS, smem, st>>>(kmap, gmap0, (const float *)q, (float *)d_q, flags, fl, n_tok,
+							       n_heads, width, scale, wk, err);
+	L1B_LAUNCH_CHECK();
+	dense_bwd_tma_kernel<1><<<grid, NTHREADS, smem, st>>>(qmap, gmap1, (const float *)k, (float *)d_k, flags, fl, n_tok,
+							       n_heads, width, scale, wk, err);
+	L1B_LAUNCH_CHECK();
+	return L1ATTN_OK;
+}
+
+// bytes of tie flags the launch above reads
+size_t dense_bwd_tma_flag_count(int bs, int n_tok, int n_heads, int width)
+{
+	return bwd_flag_layout(bs, n_tok, n_heads, width).bytes();
+}
+
+} // namespace l1b

@@ -69,7 +69,9 @@ dense_fwd_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_cons
 	constexpr int WC = CH * VEC;
 	using V = Pack<T, VEC>;
 	extern __shared__ __align__(1024) unsigned char smem_raw[];
-	unsigned char *stages = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+	// 1024-byte alignment by OFFSET into the shared array: a pointer rebuilt from an integer loses its
+	// address space and every access through it becomes a generic load, which measured ~2x slower here
+	unsigned char *stages = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
 	__shared__ __align__(8) uint64_t full_bar[NSTAGE], empty_bar[NSTAGE];
 
 	const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;

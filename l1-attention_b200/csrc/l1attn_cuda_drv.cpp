@@ -36,8 +36,10 @@ std::vector<torch::Tensor> l1attn_backward(torch::Tensor d_attn, torch::Tensor q
 		    "d_attn must be [batch, n_tokens, n_tokens, heads]");
 	const c10::cuda::CUDAGuard guard(q.device());
 	auto d_q = torch::empty_like(q), d_k = torch::empty_like(k);
-	l1b_status(l1attn_dense_bwd(d_attn.data_ptr(), q.data_ptr(), k.data_ptr(), d_q.data_ptr(), d_k.data_ptr(), bs, n,
-				    h, w, dt, l1b_stream()),
+	auto scratch = torch::empty({(long)l1attn_dense_bwd_scratch_bytes(bs, n, h, w, dt)},
+				    torch::TensorOptions().dtype(torch::kUInt8).device(q.device()));
+	l1b_status(l1attn_dense_bwd(d_attn.data_ptr(), q.data_ptr(), k.data_ptr(), d_q.data_ptr(), d_k.data_ptr(),
+				    scratch.data_ptr(), bs, n, h, w, dt, l1b_stream()),
 		   "l1attn_dense_bwd");
 	return {d_q, d_k};
 }

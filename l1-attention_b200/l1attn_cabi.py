@@ -26,7 +26,8 @@ SIGNATURES = {
     "l1attn_last_cuda_error": (_i, []),
     "l1attn_device_status": (_i, []),
     "l1attn_dense_fwd": (_i, [_vp] * 3 + [_i] * 5 + [_vp]),
-    "l1attn_dense_bwd": (_i, [_vp] * 5 + [_i] * 5 + [_vp]),
+    "l1attn_dense_bwd_scratch_bytes": (_sz, [_i] * 5),
+    "l1attn_dense_bwd": (_i, [_vp] * 6 + [_i] * 5 + [_vp]),
     "l1attn_sparse_index_bytes": (_sz, [_i] * 3),
     "l1attn_sparse_build_index": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp]),
     "l1attn_sparse_fwd": (_i, [_vp] * 7 + [_i] * 10 + [_vp]),
@@ -184,13 +185,18 @@ def dense_fwd(q, k, out=None):
     return attn
 
 
-def dense_bwd(d_attn, q, k, out=None):
+def dense_bwd(d_attn, q, k, out=None, scratch="auto"):
+    """scratch: "auto" allocates l1attn_dense_bwd_scratch_bytes() with torch, None passes NULL
+    (every tile then runs the exact loop), or a uint8 CUDA tensor of at least that size."""
     import torch
     assert q.is_cuda and q.is_contiguous() and k.is_contiguous() and d_attn.is_contiguous()
     bs, n, h, w = q.shape
     dq, dk = (torch.empty_like(q), torch.empty_like(k)) if out is None else out
-    _check(lib().l1attn_dense_bwd(_dp(d_attn), _dp(q), _dp(k), _dp(dq), _dp(dk), bs, n, h, w, _tdt(q), _stream()),
-           "l1attn_dense_bwd")
+    if isinstance(scratch, str):
+        scratch = torch.empty(lib().l1attn_dense_bwd_scratch_bytes(bs, n, h, w, _tdt(q)), dtype=torch.uint8,
+                              device=q.device)
+    _check(lib().l1attn_dense_bwd(_dp(d_attn), _dp(q), _dp(k), _dp(dq), _dp(dk), _dp(scratch), bs, n, h, w, _tdt(q),
+                                  _stream()), "l1attn_dense_bwd")
     return dq, dk
 
 

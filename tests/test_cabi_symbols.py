@@ -55,7 +55,7 @@ def test_argument_validation_needs_no_gpu():
     assert lib.l1attn_dense_fwd(p, p, p, 1, 1, 1, 1, 7, None) == -1
     assert lib.l1attn_dense_fwd(None, p, p, 1, 1, 1, 1, 0, None) == -1
     assert lib.l1attn_dense_fwd(p + 2, p, p, 1, 1, 1, 1, 0, None) == -6
-    assert lib.l1attn_dense_bwd(p, p, p, p, None, 1, 1, 1, 1, 1, None) == -1
+    assert lib.l1attn_dense_bwd(p, p, p, p, None, None, 1, 1, 1, 1, 1, None) == -1
     assert lib.l1attn_dense_fwd(p, p, p, 1, 1, 1, 0, 0, None) == -1  # width must be >= 1
     assert lib.l1attn_sparse_fwd(p, None, p, p, p, p, p, 1, 1, 1, 0, 1, 1, 1, 1, 0, 0, None) == -1
     assert lib.l1attn_sparse_fwd(p, None, p, p, None, p, p, 1, 1, 1, 1, 1, 1, 1, 1, 0, 0, None) == -1
@@ -65,7 +65,7 @@ def test_argument_validation_needs_no_gpu():
     assert lib.l1attn_expand_coo(None, 4, p, p, 0, 10, None, None) == -1
     # empty problems are fine and touch nothing
     assert lib.l1attn_dense_fwd(None, None, None, 0, 5, 2, 8, 0, None) == 0
-    assert lib.l1attn_dense_bwd(None, None, None, None, None, 3, 0, 2, 8, 1, None) == 0
+    assert lib.l1attn_dense_bwd(None, None, None, None, None, None, 3, 0, 2, 8, 1, None) == 0
 
 
 def test_size_queries():
@@ -75,6 +75,7 @@ def test_size_queries():
     assert n >= 4 * (4096 * 32 + 4097 + 131072) and n % 16 == 0
     assert lib.l1attn_sparse_bwd_scratch_bytes(8, 4096, 8, 32, 0) == 8 * 4096 * 8 * 32 * 4
     assert lib.l1attn_sparse_bwd_scratch_bytes(8, 4096, 8, 32, 1) == 8 * 4096 * 8 * 32 * 8
+    assert lib.l1attn_dense_bwd_scratch_bytes(16, 1024, 16, 64, 0) == 2 * 32 * (32 + 64)  # x and y tie flags per pass and group
     assert lib.l1attn_expand_coo_scratch_bytes(4096) == 0
     assert lib.l1attn_expand_coo_scratch_bytes(1 << 20) == (1 << 20) * 8
 
