@@ -6,57 +6,31 @@
 // in such a tie and marks the tiles that contain one (layout: dense_bwd_tiles.h); the backward
 // runs its exact loop where a marked x tile meets a marked y tile and the short loop elsewhere.
 //
-// Exact, not probabilistic: one CTA per (batch, head, group of NC width columns) builds, per
-// column, an open-addressing hash SET of the key values and one of the query values in shared
-// memory (canonical bit patterns: -0 becomes +0; NaNs are left out because they equal nothing) and
-// probes each with the other side's values, comparing full bit patterns.  Tables hold
-// 2^k >= 2*n_tok slots, so probing always ends at an empty slot.  Values are fetched in batches
-// into registers first so that the global-memory latency is paid once per batch, not once per value.
+// Exact, in two steps.  One CTA handles NC width columns of one (batch, head):
+//   1. filter: every k value sets two bits (two hash functions) of its column's bitmap in shared
+//      memory; a q value whose two bits are both set is a candidate.  With >= 128 bits per token the
+//      false-candidate rate is ~1/4096 per value, so tie-free data yields about one candidate per CTA;
+//   2. proof: every candidate value is compared, bit pattern against bit pattern, with all k values
+//      of its column (held in registers by the threads that loaded them).  Matching k rows and
+//      the candidate's q row are the rows that tie.
+// Values are canonical bit patterns (-0 becomes +0); NaNs are skipped because they equal nothing.
+// If a CTA finds more candidates than its list holds (heavy ties: padded tokens, q == k) it falls
+// back to marking conservatively: the candidate q rows it could not list and every k row of the
+// group.  Marking too much only costs speed, never correctness.
 #include "common.cuh"
 #include "dense_bwd_tiles.h"
 
 namespace l1b {
 namespace {
 
-constexpr unsigned EMPTY = 0xffffffffu; // a NaN pattern: never inserted
 constexpr int NT = 256;
-constexpr int TB = 4; // tokens per thread per batch
+constexpr int TB = 4;    // tokens per thread per batch
+constexpr int CAP = 512; // candidate list entries per CTA
 
 __device__ __forceinline__ unsigned canon(float x) { return __float_as_uint(x + 0.0f); }
-__device__ __forceinline__ unsigned slot_of(unsigned bits, int log2p) { return (bits * 2654435761u) >> (32 - log2p); }
+__device__ __forceinline__ unsigned hash1(unsigned b, int sh) { return (b * 0x9E3779B1u) >> sh; }
+__device__ __forceinline__ unsigned hash2(unsigned b, int sh) { return ((b ^ (b >> 15)) * 0xC2B2AE3Du) >> sh; }
 
-__device__ __forceinline__ void insert(unsigned *tab, unsigned mask, int log2p, float x)
-{
-	if (x != x)
-		return;
-	const unsigned bits = canon(x);
-	unsigned s = slot_of(bits, log2p);
-	for (unsigned n = 0; n <= mask; n++) { // bounded; the table is never more than half full
-		const unsigned old = atomicCAS(&tab[s], EMPTY, bits);
-		if (old == EMPTY || old == bits)
-			return;
-		s = (s + 1) & mask;
-	}
-}
-__device__ __forceinline__ bool contains(const unsigned *tab, unsigned mask, int log2p, float x)
-{
-	if (x != x)
-		return false;
-	const unsigned bits = canon(x);
-	unsigned s = slot_of(bits, log2p);
-	for (unsigned n = 0; n <= mask; n++) {
-		const unsigned v = tab[s];
-		if (v == bits)
-			return true;
-		if (v == EMPTY)
-			return false;
-		s = (s + 1) & mask;
-	}
-	return false;
-}
-
-// loads TB tokens x NC columns of one tensor for this thread (zero / NaN-free padding is not
-// needed: out-of-range tokens are marked by valid[])
 template <int NC>
 __device__ __forceinline__ void load_batch(const float *base, size_t row, int t0, int n_tok, int ncol, float (&v)[TB][NC])
 {
@@ -79,14 +53,19 @@ __device__ __forceinline__ void load_batch(const float *base, size_t row, int t0
 	}
 }
 
-// grid: bs * n_heads * ceil(width / NC) CTAs.  smem: NC * 2 tables of (1 << log2p) words.
+// grid: bs * n_heads * ceil(width / NC) CTAs.  smem: NC bitmaps of (1 << log2bits) bits.
 template <int NC>
 __global__ void __launch_bounds__(NT) dense_ties_kernel(const float *__restrict__ q, const float *__restrict__ k,
-							 unsigned char *flags, int n_tok, int n_heads, int width, int log2p,
-							 BwdFlagLayout fl)
+							 unsigned char *flags, int n_tok, int n_heads, int width,
+							 int log2bits, BwdFlagLayout fl)
 {
-	extern __shared__ unsigned tabs[]; // [NC][2][P]: [..][0] = set of k values, [..][1] = set of q values
-	const unsigned P = 1u << log2p, mask = P - 1;
+	extern __shared__ unsigned bitmap[]; // [NC][words]
+	__shared__ unsigned cand_bits[CAP];  // candidate value
+	__shared__ unsigned cand_where[CAP]; // (column << 24) | q token
+	__shared__ unsigned char cand_hit[CAP];
+	__shared__ int n_cand, overflow;
+	const unsigned words = 1u << (log2bits - 5);
+	const int sh = 32 - log2bits;
 	const int ncg = (width + NC - 1) / NC;
 	unsigned r = blockIdx.x;
 	const int w0 = int(r % ncg) * NC;
@@ -94,67 +73,133 @@ __global__ void __launch_bounds__(NT) dense_ties_kernel(const float *__restrict_
 	const int h = int(r % n_heads);
 	const int b = int(r / n_heads);
 	const int ncol = min(NC, width - w0);
-	for (unsigned i = threadIdx.x; i < unsigned(NC) * 2 * P; i += NT)
-		tabs[i] = EMPTY;
+	{
+		uint4 *bm4 = reinterpret_cast<uint4 *>(bitmap);
+		for (unsigned i = threadIdx.x; i < NC * words / 4; i += NT)
+			bm4[i] = make_uint4(0u, 0u, 0u, 0u);
+		for (int i = threadIdx.x; i < CAP; i += NT)
+			cand_hit[i] = 0;
+		if (threadIdx.x == 0) {
+			n_cand = 0;
+			overflow = 0;
+		}
+	}
 	__syncthreads();
 	const size_t row = size_t(n_heads) * width;
 	const float *qb = q + size_t(b) * n_tok * row + size_t(h) * width + w0;
 	const float *kb = k + size_t(b) * n_tok * row + size_t(h) * width + w0;
-	float qv[TB][NC], kv[TB][NC];
-	for (int t0 = threadIdx.x; t0 < n_tok; t0 += NT * TB) {
-		load_batch<NC>(qb, row, t0, n_tok, ncol, qv);
-		load_batch<NC>(kb, row, t0, n_tok, ncol, kv);
-#pragma unroll
-		for (int i = 0; i < TB; i++)
-			if (t0 + i * NT < n_tok)
-#pragma unroll
-				for (int j = 0; j < NC; j++)
-					if (j < ncol) {
-						insert(tabs + (size_t(j) * 2 + 0) * P, mask, log2p, kv[i][j]);
-						insert(tabs + (size_t(j) * 2 + 1) * P, mask, log2p, qv[i][j]);
-					}
-	}
-	__syncthreads();
 	const unsigned nhg = (n_heads + BWD_HG - 1) / BWD_HG, nws = (width + BWD_WS - 1) / BWD_WS;
 	unsigned char *xq = flags + fl.xoff(0), *xk = flags + fl.xoff(1), *yk = flags + fl.yoff(0), *yq = flags + fl.yoff(1);
+	const size_t gbase = (size_t(b) * nhg + unsigned(h) / BWD_HG) * nws;
+	const bool one_batch = n_tok <= NT * TB;
+	float v[TB][NC];
+
+	// 1a. k values -> bitmaps
 	for (int t0 = threadIdx.x; t0 < n_tok; t0 += NT * TB) {
-		if (n_tok > NT * TB) { // a single batch is still in registers
-			load_batch<NC>(qb, row, t0, n_tok, ncol, qv);
-			load_batch<NC>(kb, row, t0, n_tok, ncol, kv);
-		}
+		load_batch<NC>(kb, row, t0, n_tok, ncol, v);
 #pragma unroll
-		for (int i = 0; i < TB; i++) {
-			const int t = t0 + i * NT;
-			if (t >= n_tok)
-				continue;
+		for (int i = 0; i < TB; i++)
 #pragma unroll
 			for (int j = 0; j < NC; j++) {
-				if (j >= ncol)
-					continue;
-				const size_t g = (size_t(b) * nhg + unsigned(h) / BWD_HG) * nws + unsigned(w0 + j) / BWD_WS;
-				if (contains(tabs + (size_t(j) * 2 + 0) * P, mask, log2p, qv[i][j])) { // q row t equals some k
-					xq[g * fl.nxt + t / BWD_TX] = 1;
-					yq[g * fl.ny + t / BWD_TY] = 1;
+				const float x = v[i][j];
+				if (t0 + i * NT < n_tok && j < ncol && x == x) {
+					const unsigned bits = canon(x), h1 = hash1(bits, sh), h2 = hash2(bits, sh);
+					atomicOr(&bitmap[j * words + (h1 >> 5)], 1u << (h1 & 31));
+					atomicOr(&bitmap[j * words + (h2 >> 5)], 1u << (h2 & 31));
 				}
-				if (contains(tabs + (size_t(j) * 2 + 1) * P, mask, log2p, kv[i][j])) { // k row t equals some q
-					xk[g * fl.nxt + t / BWD_TX] = 1;
-					yk[g * fl.ny + t / BWD_TY] = 1;
+			}
+	}
+	__syncthreads();
+	// 1b. q values that pass the filter -> candidate list
+	{
+		float qv[TB][NC];
+		for (int t0 = threadIdx.x; t0 < n_tok; t0 += NT * TB) {
+			load_batch<NC>(qb, row, t0, n_tok, ncol, qv);
+#pragma unroll
+			for (int i = 0; i < TB; i++)
+#pragma unroll
+				for (int j = 0; j < NC; j++) {
+					const float x = qv[i][j];
+					const int t = t0 + i * NT;
+					if (t < n_tok && j < ncol && x == x) {
+						const unsigned bits = canon(x), h1 = hash1(bits, sh);
+						if (bitmap[j * words + (h1 >> 5)] >> (h1 & 31) & 1u) {
+							const unsigned h2 = hash2(bits, sh);
+							if (bitmap[j * words + (h2 >> 5)] >> (h2 & 31) & 1u) {
+								const int idx = atomicAdd(&n_cand, 1);
+								if (idx < CAP) {
+									cand_bits[idx] = bits;
+									cand_where[idx] = (unsigned(j) << 24) | unsigned(t);
+								} else { // list full: mark this q row without proof
+									const size_t g = gbase + unsigned(w0 + j) / BWD_WS;
+									xq[g * fl.nxt + t / BWD_TX] = 1;
+									yq[g * fl.ny + t / BWD_TY] = 1;
+									overflow = 1;
+								}
+							}
+						}
+					}
 				}
+		}
+	}
+	__syncthreads();
+	const int nc = min(n_cand, CAP);
+	if (nc == 0 && !overflow)
+		return;
+	// 2. proof: candidates against every k value of their column (k batch still in v when one_batch)
+	for (int t0 = threadIdx.x; t0 < n_tok; t0 += NT * TB) {
+		if (!one_batch)
+			load_batch<NC>(kb, row, t0, n_tok, ncol, v);
+		for (int ci = 0; ci < nc; ci++) {
+			const unsigned bits = cand_bits[ci];
+			const int col = int(cand_where[ci] >> 24);
+#pragma unroll
+			for (int i = 0; i < TB; i++) {
+				const int t = t0 + i * NT;
+#pragma unroll
+				for (int j = 0; j < NC; j++)
+					if (j == col && t < n_tok && v[i][j] == v[i][j] && canon(v[i][j]) == bits) {
+						const size_t g = gbase + unsigned(w0 + j) / BWD_WS;
+						xk[g * fl.nxt + t / BWD_TX] = 1; // k row t equals a q value
+						yk[g * fl.ny + t / BWD_TY] = 1;
+						cand_hit[ci] = 1;
+					}
+			}
+		}
+		if (overflow) { // unlisted candidates may match any k row: mark them all
+#pragma unroll
+			for (int i = 0; i < TB; i++) {
+				const int t = t0 + i * NT;
+				if (t < n_tok)
+					for (int j = 0; j < ncol; j++) {
+						const size_t g = gbase + unsigned(w0 + j) / BWD_WS;
+						xk[g * fl.nxt + t / BWD_TX] = 1;
+						yk[g * fl.ny + t / BWD_TY] = 1;
+					}
 			}
 		}
 	}
+	__syncthreads();
+	for (int ci = threadIdx.x; ci < nc; ci += NT)
+		if (cand_hit[ci]) { // proven: this q row equals some k value
+			const unsigned wv = cand_where[ci];
+			const int t = int(wv & 0xffffffu), j = int(wv >> 24);
+			const size_t g = gbase + unsigned(w0 + j) / BWD_WS;
+			xq[g * fl.nxt + t / BWD_TX] = 1;
+			yq[g * fl.ny + t / BWD_TY] = 1;
+		}
 }
 
 template <int NC>
-int launch_nc(const float *q, const float *k, unsigned char *flags, int bs, int n_tok, int n_heads, int width, int log2p,
+int launch_nc(const float *q, const float *k, unsigned char *flags, int bs, int n_tok, int n_heads, int width, int log2bits,
 	      const BwdFlagLayout &fl, cudaStream_t st)
 {
 	const long long grid = (long long)bs * n_heads * ((width + NC - 1) / NC);
 	if (grid > 0x7fffffffLL)
 		return 1;
-	const size_t smem = size_t(NC) * 2 * (size_t(1) << log2p) * 4;
+	const size_t smem = size_t(NC) * (size_t(1) << log2bits) / 8;
 	L1B_CUDA(cudaFuncSetAttribute(dense_ties_kernel<NC>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
-	dense_ties_kernel<NC><<<unsigned(grid), NT, smem, st>>>(q, k, flags, n_tok, n_heads, width, log2p, fl);
+	dense_ties_kernel<NC><<<unsigned(grid), NT, smem, st>>>(q, k, flags, n_tok, n_heads, width, log2bits, fl);
 	L1B_LAUNCH_CHECK();
 	return L1ATTN_OK;
 }
@@ -162,25 +207,24 @@ int launch_nc(const float *q, const float *k, unsigned char *flags, int bs, int 
 } // namespace
 
 // Fills the flag arrays (device, bwd_flag_layout(...).bytes() bytes).  Returns L1ATTN_OK, a negative
-// error, or 1 when n_tok is too large for the shared-memory tables (the caller then runs every
-// tile with the exact loop).
+// error, or 1 when the detector does not apply (token index beyond 24 bits, width not a multiple of 4);
+// the caller then runs every tile with the exact loop.
 int dense_ties_launch(const float *q, const float *k, unsigned char *flags, int bs, int n_tok, int n_heads, int width,
 		      cudaStream_t st)
 {
-	int log2p = 1;
-	while ((1 << log2p) < 2 * n_tok)
-		log2p++;
-	const size_t per_col = size_t(2) * (size_t(1) << log2p) * 4;
-	const size_t budget = 200 * 1024;
-	if (per_col > budget || width % 4 != 0)
+	if (width % 4 != 0 || n_tok >= (1 << 24))
 		return 1;
+	int log2bits = 15; // >= 128 bits per token, between 4 KiB and 64 KiB per column
+	while (log2bits < 19 && (1 << log2bits) < 128 * n_tok)
+		log2bits++;
+	const size_t per_col = (size_t(1) << log2bits) / 8;
 	const BwdFlagLayout fl = bwd_flag_layout(bs, n_tok, n_heads, width);
 	L1B_CUDA(cudaMemsetAsync(flags, 0, fl.bytes(), st));
-	if (4 * per_col <= budget / 3) // three CTAs of four columns per SM
-		return launch_nc<4>(q, k, flags, bs, n_tok, n_heads, width, log2p, fl, st);
-	if (2 * per_col <= budget)
-		return launch_nc<2>(q, k, flags, bs, n_tok, n_heads, width, log2p, fl, st);
-	return launch_nc<1>(q, k, flags, bs, n_tok, n_heads, width, log2p, fl, st);
+	if (4 * per_col <= 96 * 1024)
+		return launch_nc<4>(q, k, flags, bs, n_tok, n_heads, width, log2bits, fl, st);
+	if (2 * per_col <= 96 * 1024)
+		return launch_nc<2>(q, k, flags, bs, n_tok, n_heads, width, log2bits, fl, st);
+	return launch_nc<1>(q, k, flags, bs, n_tok, n_heads, width, log2bits, fl, st);
 }
 
 } // namespace l1b

@@ -99,6 +99,41 @@ def test_ties_exact(dtype):
     assert_close(dk, rk, 2e-7 if dtype == np.float32 else 1e-14, "dk ties")
 
 
+@pytest.mark.parametrize("kind", ["sparse_ties", "padded", "q_is_k", "grid"])
+def test_fast_backward_tie_handling(kind):
+    """fp32 shapes that take the compare-form backward (16-byte rows): a handful of planted ties, many
+    zero-padded tokens (more candidates than the detector lists), q == k, and values on a coarse grid
+    (ties everywhere).  The result must match the oracle as if every term had used sign(0) = 0."""
+    from oracle import oracle
+    cabi = _cabi()
+    rng = np.random.RandomState(21)
+    shape = (2, 200, 8, 64)
+    q = rng.standard_normal(shape).astype(np.float32)
+    k = rng.standard_normal(shape).astype(np.float32)
+    if kind == "sparse_ties":
+        for _ in range(7):
+            b, t, s, h, w = (rng.randint(n) for n in (2, 200, 200, 8, 64))
+            k[b, s, h, w] = q[b, t, h, w]
+        k[1, 5, 3, 7] = -0.0
+        q[1, 9, 3, 7] = 0.0  # +0 == -0 is a tie too
+    elif kind == "padded":
+        q[:, 120:] = 0
+        k[:, 90:] = 0
+    elif kind == "q_is_k":
+        k = q.copy()
+    else:
+        q, k = np.round(q * 2) / 2, np.round(k * 2) / 2
+    g = rng.standard_normal((2, 200, 200, 8)).astype(np.float32)
+    dq, dk = (x.cpu().numpy() for x in cabi.dense_bwd(_dev(g), _dev(q), _dev(k)))
+    rq, rk = oracle.dense_bwd(g.astype(np.float64), q.astype(np.float64), k.astype(np.float64))
+    assert_close(dq, rq, 1e-5, "dq " + kind)
+    assert_close(dk, rk, 1e-5, "dk " + kind)
+    # without scratch every tile takes the exact loop: same answer
+    dq2, dk2 = (x.cpu().numpy() for x in cabi.dense_bwd(_dev(g), _dev(q), _dev(k), scratch=None))
+    assert_close(dq2, rq, 1e-5, "dq exact " + kind)
+    assert_close(dk2, rk, 1e-5, "dk exact " + kind)
+
+
 def test_deterministic():
     cabi = _cabi()
     q, k, g = _rand((2, 96, 16, 64), np.float32, 11)
