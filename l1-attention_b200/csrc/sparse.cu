@@ -66,6 +66,10 @@ __device__ __forceinline__ bool decode(const SparseArgs &a, Who &w)
 	return true;
 }
 
+// Edge loops walk the slots / incoming edges U at a time: the U gathered rows are requested before
+// any of them is used, so U row fetches (L2 latency each) are in flight per warp instead of one.
+constexpr int U = 4;
+
 // ---- forward, dst pass: scores -> exp -> (+1)-softmax -> attn, vo[dst] = sum_r a_r v[src_r] ----
 template <typename T, int VEC>
 __global__ void __launch_bounds__(256) sparse_fwd_dst_kernel(SparseArgs a, const T *__restrict__ v,
@@ -84,25 +88,37 @@ __global__ void __launch_bounds__(256) sparse_fwd_dst_kernel(SparseArgs a, const
 	const int step = a.lph * VEC;
 
 	T denom = T(1);
-	for (int r = 0; r < dm; r++) {
-		const int src = slots[r];
-		T e = T(0);
-		if (src >= 0) {
-			const T *krow = k + ((tokrow + src) * H + hh) * W;
-			T part = T(0);
-			for (int x = w.li * VEC; x < W; x += step) {
-				const Pack<T, VEC> qv = ldv<T, VEC>(qrow + x, w.head_ok);
-				const Pack<T, VEC> kv = ldv<T, VEC>(krow + x, w.head_ok);
+	for (int r0 = 0; r0 < dm; r0 += U) {
+		int src[U];
+		T part[U];
+#pragma unroll
+		for (int u = 0; u < U; u++) {
+			src[u] = r0 + u < dm ? slots[r0 + u] : -1;
+			part[u] = T(0);
+		}
+		for (int x = w.li * VEC; x < W; x += step) {
+			const Pack<T, VEC> qv = ldv<T, VEC>(qrow + x, w.head_ok);
+			Pack<T, VEC> kv[U];
+#pragma unroll
+			for (int u = 0; u < U; u++)
+				kv[u] = ldv<T, VEC>(k + ((tokrow + (src[u] < 0 ? 0 : src[u])) * H + hh) * W + x,
+						    w.head_ok && src[u] >= 0);
+#pragma unroll
+			for (int u = 0; u < U; u++)
 #pragma unroll
 				for (int i = 0; i < VEC; i++)
-					part += absdiff(qv.v[i], kv.v[i]);
-			}
-			part = group_sum(part, a.lph);
-			e = exp_t(part * scale);
-			denom += e;
+					part[u] += absdiff(qv.v[i], kv[u].v[i]);
 		}
-		if (w.li == 0 && w.head_ok)
-			arow[size_t(r) * H] = e;
+#pragma unroll
+		for (int u = 0; u < U; u++)
+			part[u] = group_sum(part[u], a.lph);
+#pragma unroll
+		for (int u = 0; u < U; u++) {
+			const T e = src[u] >= 0 ? exp_t(part[u] * scale) : T(0);
+			denom += e;
+			if (w.li == 0 && w.head_ok && r0 + u < dm)
+				arow[size_t(r0 + u) * H] = e;
+		}
 	}
 	__syncwarp();
 	if (a.use_softmax && w.head_ok)
@@ -113,15 +129,21 @@ __global__ void __launch_bounds__(256) sparse_fwd_dst_kernel(SparseArgs a, const
 	T *orow = vo + ((tokrow + dst) * H + hh) * Wv;
 	for (int x = w.li * VEC; x < Wv; x += step) {
 		Pack<T, VEC> acc = ldv<T, VEC>(nullptr, false);
-		for (int r = 0; r < dm; r++) {
-			const int src = slots[r];
-			if (src < 0)
-				continue;
-			const T ar = w.head_ok ? arow[size_t(r) * H] : T(0);
-			const Pack<T, VEC> vv = ldv<T, VEC>(v + ((tokrow + src) * H + hh) * Wv + x, w.head_ok);
+		for (int r0 = 0; r0 < dm; r0 += U) {
+			T ar[U];
+			Pack<T, VEC> vv[U];
 #pragma unroll
-			for (int i = 0; i < VEC; i++)
-				acc.v[i] += ar * vv.v[i];
+			for (int u = 0; u < U; u++) {
+				const int src = r0 + u < dm ? slots[r0 + u] : -1;
+				const bool ok = w.head_ok && src >= 0;
+				ar[u] = ok ? arow[size_t(r0 + u) * H] : T(0);
+				vv[u] = ldv<T, VEC>(v + ((tokrow + (src < 0 ? 0 : src)) * H + hh) * Wv + x, ok);
+			}
+#pragma unroll
+			for (int u = 0; u < U; u++)
+#pragma unroll
+				for (int i = 0; i < VEC; i++)
+					acc.v[i] += ar[u] * vv[u].v[i];
 		}
 		if (w.head_ok)
 			*reinterpret_cast<Pack<T, VEC> *>(orow + x) = acc;
@@ -145,14 +167,21 @@ __global__ void __launch_bounds__(256) sparse_fwd_src_kernel(SparseArgs a, const
 	T *orow = vo + ((tokrow + src) * H + w.h) * Wv;
 	for (int x = w.li * VEC; x < Wv; x += step) {
 		Pack<T, VEC> acc = ldv<T, VEC>(nullptr, false);
-		for (int e = e0; e < e1; e++) {
-			const int slot = a.csc_slot[e];
-			const int dst = slot / dm;
-			const T ar = attn[(tokrow * dm + slot) * H + w.h];
-			const Pack<T, VEC> vv = ldv<T, VEC>(vb + ((tokrow + dst) * H + w.h) * Wv + x, true);
+		for (int eb = e0; eb < e1; eb += U) {
+			T ar[U];
+			Pack<T, VEC> vv[U];
 #pragma unroll
-			for (int i = 0; i < VEC; i++)
-				acc.v[i] += ar * vv.v[i];
+			for (int u = 0; u < U; u++) {
+				const bool ok = eb + u < e1;
+				const int slot = ok ? a.csc_slot[eb + u] : 0;
+				ar[u] = ok ? attn[(tokrow * dm + slot) * H + w.h] : T(0);
+				vv[u] = ldv<T, VEC>(vb + ((tokrow + slot / dm) * H + w.h) * Wv + x, ok);
+			}
+#pragma unroll
+			for (int u = 0; u < U; u++)
+#pragma unroll
+				for (int i = 0; i < VEC; i++)
+					acc.v[i] += ar[u] * vv[u].v[i];
 		}
 		Pack<T, VEC> cur = ldv<T, VEC>(orow + x, true);
 #pragma unroll
@@ -186,32 +215,53 @@ __global__ void __launch_bounds__(256) sparse_bwd_dst_kernel(SparseArgs a, const
 	const int32_t *slots = a.slot_src + size_t(dst) * dm;
 	const int step = a.lph * VEC;
 	const T *gdst = dvo + ((tokrow + dst) * H + hh) * Wv;
+	const T *bdst = a.bidi ? vb + ((tokrow + dst) * H + hh) * Wv : nullptr;
 
 	T S = T(0);
-	for (int r = 0; r < dm; r++) {
-		const int src = slots[r];
-		if (src < 0)
-			continue;
-		T part = T(0);
-		for (int x = w.li * VEC; x < Wv; x += step) {
-			const Pack<T, VEC> vv = ldv<T, VEC>(v + ((tokrow + src) * H + hh) * Wv + x, w.head_ok);
-			const Pack<T, VEC> gv = ldv<T, VEC>(gdst + x, w.head_ok);
+	for (int r0 = 0; r0 < dm; r0 += U) {
+		int src[U];
+		T part[U];
 #pragma unroll
-			for (int i = 0; i < VEC; i++)
-				part += vv.v[i] * gv.v[i];
-			if (a.bidi) {
-				const Pack<T, VEC> bv = ldv<T, VEC>(vb + ((tokrow + dst) * H + hh) * Wv + x, w.head_ok);
-				const Pack<T, VEC> gs = ldv<T, VEC>(dvo + ((tokrow + src) * H + hh) * Wv + x, w.head_ok);
+		for (int u = 0; u < U; u++) {
+			src[u] = r0 + u < dm ? slots[r0 + u] : -1;
+			part[u] = T(0);
+		}
+		for (int x = w.li * VEC; x < Wv; x += step) {
+			const Pack<T, VEC> gv = ldv<T, VEC>(gdst + x, w.head_ok);
+			Pack<T, VEC> vv[U], gs[U];
+#pragma unroll
+			for (int u = 0; u < U; u++) {
+				const bool ok = w.head_ok && src[u] >= 0;
+				const size_t off = ((tokrow + (src[u] < 0 ? 0 : src[u])) * H + hh) * Wv + x;
+				vv[u] = ldv<T, VEC>(v + off, ok);
+				gs[u] = ldv<T, VEC>(dvo + off, ok && a.bidi);
+			}
+#pragma unroll
+			for (int u = 0; u < U; u++)
 #pragma unroll
 				for (int i = 0; i < VEC; i++)
-					part += bv.v[i] * gs.v[i];
+					part[u] += vv[u].v[i] * gv.v[i];
+			if (a.bidi) {
+				const Pack<T, VEC> bv = ldv<T, VEC>(bdst + x, w.head_ok);
+#pragma unroll
+				for (int u = 0; u < U; u++)
+#pragma unroll
+					for (int i = 0; i < VEC; i++)
+						part[u] += bv.v[i] * gs[u].v[i];
 			}
 		}
-		const T ds = group_sum(part, a.lph);
-		const T ar = w.head_ok ? arow[size_t(r) * H] : T(0);
-		S += ar * ds;
-		if (w.li == 0 && w.head_ok)
-			xrow[size_t(r) * H] = ds;
+#pragma unroll
+		for (int u = 0; u < U; u++)
+			part[u] = group_sum(part[u], a.lph);
+#pragma unroll
+		for (int u = 0; u < U; u++) {
+			if (src[u] < 0)
+				continue;
+			const T ar = w.head_ok ? arow[size_t(r0 + u) * H] : T(0);
+			S += ar * part[u];
+			if (w.li == 0 && w.head_ok)
+				xrow[size_t(r0 + u) * H] = part[u];
+		}
 	}
 	__syncwarp();
 	if (w.head_ok)
@@ -228,15 +278,22 @@ __global__ void __launch_bounds__(256) sparse_bwd_dst_kernel(SparseArgs a, const
 	for (int x = w.li * VEC; x < W; x += step) {
 		const Pack<T, VEC> qv = ldv<T, VEC>(qrow + x, w.head_ok);
 		Pack<T, VEC> acc = ldv<T, VEC>(nullptr, false);
-		for (int r = 0; r < dm; r++) {
-			const int src = slots[r];
-			if (src < 0)
-				continue;
-			const T dxr = w.head_ok ? xrow[size_t(r) * H] : T(0);
-			const Pack<T, VEC> kv = ldv<T, VEC>(k + ((tokrow + src) * H + hh) * W + x, w.head_ok);
+		for (int r0 = 0; r0 < dm; r0 += U) {
+			T dxr[U];
+			Pack<T, VEC> kv[U];
 #pragma unroll
-			for (int i = 0; i < VEC; i++)
-				acc.v[i] += sign_apply(qv.v[i] - kv.v[i], dxr);
+			for (int u = 0; u < U; u++) {
+				const int src = r0 + u < dm ? slots[r0 + u] : -1;
+				const bool ok = w.head_ok && src >= 0;
+				dxr[u] = ok ? xrow[size_t(r0 + u) * H] : T(0);
+				// a missing edge reads q itself: difference 0, contributes nothing
+				kv[u] = ok ? ldv<T, VEC>(k + ((tokrow + src) * H + hh) * W + x, true) : qv;
+			}
+#pragma unroll
+			for (int u = 0; u < U; u++)
+#pragma unroll
+				for (int i = 0; i < VEC; i++)
+					acc.v[i] += sign_apply(qv.v[i] - kv[u].v[i], dxr[u]);
 		}
 		if (w.head_ok) {
 #pragma unroll
@@ -249,15 +306,21 @@ __global__ void __launch_bounds__(256) sparse_bwd_dst_kernel(SparseArgs a, const
 		T *brow = d_vb + ((tokrow + dst) * H + hh) * Wv;
 		for (int x = w.li * VEC; x < Wv; x += step) {
 			Pack<T, VEC> acc = ldv<T, VEC>(nullptr, false);
-			for (int r = 0; r < dm; r++) {
-				const int src = slots[r];
-				if (src < 0)
-					continue;
-				const T ar = w.head_ok ? arow[size_t(r) * H] : T(0);
-				const Pack<T, VEC> gs = ldv<T, VEC>(dvo + ((tokrow + src) * H + hh) * Wv + x, w.head_ok);
+			for (int r0 = 0; r0 < dm; r0 += U) {
+				T ar[U];
+				Pack<T, VEC> gs[U];
 #pragma unroll
-				for (int i = 0; i < VEC; i++)
-					acc.v[i] += ar * gs.v[i];
+				for (int u = 0; u < U; u++) {
+					const int src = r0 + u < dm ? slots[r0 + u] : -1;
+					const bool ok = w.head_ok && src >= 0;
+					ar[u] = ok ? arow[size_t(r0 + u) * H] : T(0);
+					gs[u] = ldv<T, VEC>(dvo + ((tokrow + (src < 0 ? 0 : src)) * H + hh) * Wv + x, ok);
+				}
+#pragma unroll
+				for (int u = 0; u < U; u++)
+#pragma unroll
+					for (int i = 0; i < VEC; i++)
+						acc.v[i] += ar[u] * gs[u].v[i];
 			}
 			if (w.head_ok)
 				*reinterpret_cast<Pack<T, VEC> *>(brow + x) = acc;
@@ -284,14 +347,21 @@ __global__ void __launch_bounds__(256) sparse_bwd_src_kernel(SparseArgs a, const
 	T *vrow = d_v + ((tokrow + src) * H + w.h) * Wv;
 	for (int x = w.li * VEC; x < Wv; x += step) {
 		Pack<T, VEC> acc = ldv<T, VEC>(nullptr, false);
-		for (int e = e0; e < e1; e++) {
-			const int slot = a.csc_slot[e];
-			const int dst = slot / dm;
-			const T ar = attn[(tokrow * dm + slot) * H + w.h];
-			const Pack<T, VEC> gv = ldv<T, VEC>(dvo + ((tokrow + dst) * H + w.h) * Wv + x, true);
+		for (int eb = e0; eb < e1; eb += U) {
+			T ar[U];
+			Pack<T, VEC> gv[U];
 #pragma unroll
-			for (int i = 0; i < VEC; i++)
-				acc.v[i] += ar * gv.v[i];
+			for (int u = 0; u < U; u++) {
+				const bool ok = eb + u < e1;
+				const int slot = ok ? a.csc_slot[eb + u] : 0;
+				ar[u] = ok ? attn[(tokrow * dm + slot) * H + w.h] : T(0);
+				gv[u] = ldv<T, VEC>(dvo + ((tokrow + slot / dm) * H + w.h) * Wv + x, ok);
+			}
+#pragma unroll
+			for (int u = 0; u < U; u++)
+#pragma unroll
+				for (int i = 0; i < VEC; i++)
+					acc.v[i] += ar[u] * gv[u].v[i];
 		}
 		*reinterpret_cast<Pack<T, VEC> *>(vrow + x) = acc;
 	}
@@ -300,14 +370,22 @@ __global__ void __launch_bounds__(256) sparse_bwd_src_kernel(SparseArgs a, const
 	for (int x = w.li * VEC; x < W; x += step) {
 		const Pack<T, VEC> kv = ldv<T, VEC>(krow + x, true);
 		Pack<T, VEC> acc = ldv<T, VEC>(nullptr, false);
-		for (int e = e0; e < e1; e++) {
-			const int slot = a.csc_slot[e];
-			const int dst = slot / dm;
-			const T dxr = dx[(tokrow * dm + slot) * H + w.h];
-			const Pack<T, VEC> qv = ldv<T, VEC>(q + ((tokrow + dst) * H + w.h) * W + x, true);
+		for (int eb = e0; eb < e1; eb += U) {
+			T dxr[U];
+			Pack<T, VEC> qv[U];
 #pragma unroll
-			for (int i = 0; i < VEC; i++)
-				acc.v[i] += sign_apply(qv.v[i] - kv.v[i], dxr);
+			for (int u = 0; u < U; u++) {
+				const bool ok = eb + u < e1;
+				const int slot = ok ? a.csc_slot[eb + u] : 0;
+				dxr[u] = ok ? dx[(tokrow * dm + slot) * H + w.h] : T(0);
+				// past the end of the list read k itself: difference 0, contributes nothing
+				qv[u] = ok ? ldv<T, VEC>(q + ((tokrow + slot / dm) * H + w.h) * W + x, true) : kv;
+			}
+#pragma unroll
+			for (int u = 0; u < U; u++)
+#pragma unroll
+				for (int i = 0; i < VEC; i++)
+					acc.v[i] += sign_apply(qv[u].v[i] - kv.v[i], dxr[u]);
 		}
 #pragma unroll
 		for (int i = 0; i < VEC; i++)
