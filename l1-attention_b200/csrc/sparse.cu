@@ -35,10 +35,17 @@ template <typename T, int VEC> __device__ __forceinline__ Pack<T, VEC> ldv(const
 	return r;
 }
 
-template <typename T> __device__ __forceinline__ T group_sum(T x, int lph)
+// LPHC > 0: lanes per head known at compile time (the shuffles unroll, index math folds); 0: run-time value
+template <int LPHC, typename T> __device__ __forceinline__ T group_sum(T x, int lph)
 {
-	for (int o = lph >> 1; o > 0; o >>= 1)
-		x += __shfl_xor_sync(0xffffffffu, x, o);
+	if (LPHC > 0) {
+#pragma unroll
+		for (int o = LPHC >> 1; o > 0; o >>= 1)
+			x += __shfl_xor_sync(0xffffffffu, x, o);
+	} else {
+		for (int o = lph >> 1; o > 0; o >>= 1)
+			x += __shfl_xor_sync(0xffffffffu, x, o);
+	}
 	return x;
 }
 
@@ -47,10 +54,11 @@ struct Who {
 	int b, tok, h, li;
 	bool head_ok;
 };
-__device__ __forceinline__ bool decode(const SparseArgs &a, Who &w)
+template <int LPHC> __device__ __forceinline__ bool decode(const SparseArgs &a, Who &w)
 {
 	const int lane = threadIdx.x & 31;
-	const int hpw = 32 / a.lph;
+	const int lph = LPHC > 0 ? LPHC : a.lph;
+	const int hpw = 32 / lph;
 	const int nhc = (a.n_heads + hpw - 1) / hpw;
 	long long gw = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
 	const int hc = int(gw % nhc);
@@ -60,8 +68,8 @@ __device__ __forceinline__ bool decode(const SparseArgs &a, Who &w)
 	if (b >= a.bs)
 		return false;
 	w.b = int(b);
-	w.li = lane % a.lph;
-	w.h = hc * hpw + lane / a.lph;
+	w.li = lane % lph;
+	w.h = hc * hpw + lane / lph;
 	w.head_ok = w.h < a.n_heads;
 	return true;
 }
@@ -71,13 +79,13 @@ __device__ __forceinline__ bool decode(const SparseArgs &a, Who &w)
 constexpr int U = 4;
 
 // ---- forward, dst pass: scores -> exp -> (+1)-softmax -> attn, vo[dst] = sum_r a_r v[src_r] ----
-template <typename T, int VEC>
+template <typename T, int VEC, int LPHC>
 __global__ void __launch_bounds__(256) sparse_fwd_dst_kernel(SparseArgs a, const T *__restrict__ v,
 							      const T *__restrict__ q, const T *__restrict__ k,
 							      T *__restrict__ vo, T *attn, T scale)
 {
 	Who w;
-	if (!decode(a, w))
+	if (!decode<LPHC>(a, w))
 		return;
 	const int dst = w.tok, H = a.n_heads, W = a.width, Wv = a.v_width, dm = a.dm;
 	const int hh = w.head_ok ? w.h : 0;
@@ -85,7 +93,8 @@ __global__ void __launch_bounds__(256) sparse_fwd_dst_kernel(SparseArgs a, const
 	const T *qrow = q + ((tokrow + dst) * H + hh) * W;
 	T *arow = attn + ((tokrow + dst) * dm) * H + hh;
 	const int32_t *slots = a.slot_src + size_t(dst) * dm;
-	const int step = a.lph * VEC;
+	const int lph = LPHC > 0 ? LPHC : a.lph;
+	const int step = lph * VEC;
 
 	T denom = T(1);
 	for (int r0 = 0; r0 < dm; r0 += U) {
@@ -111,7 +120,7 @@ __global__ void __launch_bounds__(256) sparse_fwd_dst_kernel(SparseArgs a, const
 		}
 #pragma unroll
 		for (int u = 0; u < U; u++)
-			part[u] = group_sum(part[u], a.lph);
+			part[u] = group_sum<LPHC>(part[u], lph);
 #pragma unroll
 		for (int u = 0; u < U; u++) {
 			const T e = src[u] >= 0 ? exp_t(part[u] * scale) : T(0);
@@ -122,7 +131,7 @@ __global__ void __launch_bounds__(256) sparse_fwd_dst_kernel(SparseArgs a, const
 	}
 	__syncwarp();
 	if (a.use_softmax && w.head_ok)
-		for (int r = w.li; r < dm; r += a.lph)
+		for (int r = w.li; r < dm; r += lph)
 			arow[size_t(r) * H] = arow[size_t(r) * H] / denom;
 	__syncwarp();
 
@@ -151,19 +160,20 @@ __global__ void __launch_bounds__(256) sparse_fwd_dst_kernel(SparseArgs a, const
 }
 
 // ---- forward, src pass (bidi only): vo[src] += sum_{incoming (dst,r)} a[dst][r] * vb[dst] ----
-template <typename T, int VEC>
+template <typename T, int VEC, int LPHC>
 __global__ void __launch_bounds__(256) sparse_fwd_src_kernel(SparseArgs a, const T *__restrict__ vb,
 							      const T *__restrict__ attn, T *vo)
 {
 	Who w;
-	if (!decode(a, w))
+	if (!decode<LPHC>(a, w))
 		return;
 	if (!w.head_ok)
 		return;
 	const int src = w.tok, H = a.n_heads, Wv = a.v_width, dm = a.dm;
 	const size_t tokrow = size_t(w.b) * a.n_tok;
 	const int e0 = a.csc_off[src], e1 = a.csc_off[src + 1];
-	const int step = a.lph * VEC;
+	const int lph = LPHC > 0 ? LPHC : a.lph;
+	const int step = lph * VEC;
 	T *orow = vo + ((tokrow + src) * H + w.h) * Wv;
 	for (int x = w.li * VEC; x < Wv; x += step) {
 		Pack<T, VEC> acc = ldv<T, VEC>(nullptr, false);
@@ -196,7 +206,7 @@ __global__ void __launch_bounds__(256) sparse_fwd_src_kernel(SparseArgs a, const
 //   softmax: dx_r = a_r (ds_r - sum_j a_j ds_j)   [same as the reference's Jacobian product,
 //            cuda/l1attn_sparse_cuda_kernel.cu:256-295, without its O(dst_mxlen^2) loop]
 //   else:    dx_r = a_r ds_r
-template <typename T, int VEC>
+template <typename T, int VEC, int LPHC>
 __global__ void __launch_bounds__(256) sparse_bwd_dst_kernel(SparseArgs a, const T *__restrict__ dvo,
 							      const T *__restrict__ v, const T *__restrict__ vb,
 							      const T *__restrict__ q, const T *__restrict__ k,
@@ -204,7 +214,7 @@ __global__ void __launch_bounds__(256) sparse_bwd_dst_kernel(SparseArgs a, const
 							      T *__restrict__ d_vb, T scale)
 {
 	Who w;
-	if (!decode(a, w))
+	if (!decode<LPHC>(a, w))
 		return;
 	const int dst = w.tok, H = a.n_heads, W = a.width, Wv = a.v_width, dm = a.dm;
 	const int hh = w.head_ok ? w.h : 0;
@@ -213,7 +223,8 @@ __global__ void __launch_bounds__(256) sparse_bwd_dst_kernel(SparseArgs a, const
 	const T *arow = attn + aoff;
 	T *xrow = dx + aoff;
 	const int32_t *slots = a.slot_src + size_t(dst) * dm;
-	const int step = a.lph * VEC;
+	const int lph = LPHC > 0 ? LPHC : a.lph;
+	const int step = lph * VEC;
 	const T *gdst = dvo + ((tokrow + dst) * H + hh) * Wv;
 	const T *bdst = a.bidi ? vb + ((tokrow + dst) * H + hh) * Wv : nullptr;
 
@@ -252,7 +263,7 @@ __global__ void __launch_bounds__(256) sparse_bwd_dst_kernel(SparseArgs a, const
 		}
 #pragma unroll
 		for (int u = 0; u < U; u++)
-			part[u] = group_sum(part[u], a.lph);
+			part[u] = group_sum<LPHC>(part[u], lph);
 #pragma unroll
 		for (int u = 0; u < U; u++) {
 			if (src[u] < 0)
@@ -265,7 +276,7 @@ __global__ void __launch_bounds__(256) sparse_bwd_dst_kernel(SparseArgs a, const
 	}
 	__syncwarp();
 	if (w.head_ok)
-		for (int r = w.li; r < dm; r += a.lph) {
+		for (int r = w.li; r < dm; r += lph) {
 			if (slots[r] < 0)
 				continue;
 			const T ar = arow[size_t(r) * H], ds = xrow[size_t(r) * H];
@@ -329,21 +340,22 @@ __global__ void __launch_bounds__(256) sparse_bwd_dst_kernel(SparseArgs a, const
 }
 
 // ---- backward, src pass: d_v[src] = sum a dvo[dst];  d_k[src] = -scale sum sign(q[dst]-k[src]) dx ----
-template <typename T, int VEC>
+template <typename T, int VEC, int LPHC>
 __global__ void __launch_bounds__(256) sparse_bwd_src_kernel(SparseArgs a, const T *__restrict__ dvo,
 							      const T *__restrict__ q, const T *__restrict__ k,
 							      const T *__restrict__ attn, const T *__restrict__ dx,
 							      T *__restrict__ d_v, T *__restrict__ d_k, T scale)
 {
 	Who w;
-	if (!decode(a, w))
+	if (!decode<LPHC>(a, w))
 		return;
 	if (!w.head_ok)
 		return;
 	const int src = w.tok, H = a.n_heads, W = a.width, Wv = a.v_width, dm = a.dm;
 	const size_t tokrow = size_t(w.b) * a.n_tok;
 	const int e0 = a.csc_off[src], e1 = a.csc_off[src + 1];
-	const int step = a.lph * VEC;
+	const int lph = LPHC > 0 ? LPHC : a.lph;
+	const int step = lph * VEC;
 	T *vrow = d_v + ((tokrow + src) * H + w.h) * Wv;
 	for (int x = w.li * VEC; x < Wv; x += step) {
 		Pack<T, VEC> acc = ldv<T, VEC>(nullptr, false);
@@ -418,19 +430,34 @@ template <typename T, int VEC>
 int fwd_t(SparseArgs a, const T *v, const T *vb, const T *q, const T *k, T *vo, T *attn, cudaStream_t st)
 {
 	const int mw = a.width > a.v_width ? a.width : a.v_width;
-	a.lph = pow2_ceil((mw + VEC - 1) / VEC);
+	a.lph = pow2_ceil((mw + 4 * VEC - 1) / (4 * VEC)); // four 16-byte vectors per lane: fewer shuffle rounds and less index math per term
 	if (a.lph > 32)
 		a.lph = 32;
 	const Grid g = grid_for(a);
 	if (!g.ok)
 		return L1ATTN_ERR_SHAPE;
 	const T scale = T(-1.0 / sqrt(double(a.width)));
-	sparse_fwd_dst_kernel<T, VEC><<<g.blocks, 256, 0, st>>>(a, v, q, k, vo, attn, scale);
-	L1B_LAUNCH_CHECK();
-	if (a.bidi) {
-		sparse_fwd_src_kernel<T, VEC><<<g.blocks, 256, 0, st>>>(a, vb, attn, vo);
-		L1B_LAUNCH_CHECK();
-	}
+	// lanes per head as a compile-time constant for the common widths (16-byte vectors, 32..128+ columns)
+#define L1B_FWD(LP)                                                                                      \
+	do {                                                                                             \
+		sparse_fwd_dst_kernel<T, VEC, LP><<<g.blocks, 256, 0, st>>>(a, v, q, k, vo, attn, scale); \
+		L1B_LAUNCH_CHECK();                                                                      \
+		if (a.bidi) {                                                                            \
+			sparse_fwd_src_kernel<T, VEC, LP><<<g.blocks, 256, 0, st>>>(a, vb, attn, vo);     \
+			L1B_LAUNCH_CHECK();                                                              \
+		}                                                                                        \
+	} while (0)
+	if (VEC > 1 && a.lph == 4)
+		L1B_FWD(4);
+	else if (VEC > 1 && a.lph == 8)
+		L1B_FWD(8);
+	else if (VEC > 1 && a.lph == 16)
+		L1B_FWD(16);
+	else if (VEC > 1 && a.lph == 32)
+		L1B_FWD(32);
+	else
+		L1B_FWD(0);
+#undef L1B_FWD
 	return L1ATTN_OK;
 }
 
@@ -439,17 +466,31 @@ int bwd_t(SparseArgs a, const T *dvo, const T *v, const T *vb, const T *q, const
 	  T *d_vb, T *d_q, T *d_k, T *dx, cudaStream_t st)
 {
 	const int mw = a.width > a.v_width ? a.width : a.v_width;
-	a.lph = pow2_ceil((mw + VEC - 1) / VEC);
+	a.lph = pow2_ceil((mw + 4 * VEC - 1) / (4 * VEC)); // four 16-byte vectors per lane: fewer shuffle rounds and less index math per term
 	if (a.lph > 32)
 		a.lph = 32;
 	const Grid g = grid_for(a);
 	if (!g.ok)
 		return L1ATTN_ERR_SHAPE;
 	const T scale = T(-1.0 / sqrt(double(a.width)));
-	sparse_bwd_dst_kernel<T, VEC><<<g.blocks, 256, 0, st>>>(a, dvo, v, vb, q, k, attn, dx, d_q, d_vb, scale);
-	L1B_LAUNCH_CHECK();
-	sparse_bwd_src_kernel<T, VEC><<<g.blocks, 256, 0, st>>>(a, dvo, q, k, attn, dx, d_v, d_k, scale);
-	L1B_LAUNCH_CHECK();
+#define L1B_BWD(LP)                                                                                                       \
+	do {                                                                                                              \
+		sparse_bwd_dst_kernel<T, VEC, LP><<<g.blocks, 256, 0, st>>>(a, dvo, v, vb, q, k, attn, dx, d_q, d_vb, scale); \
+		L1B_LAUNCH_CHECK();                                                                                       \
+		sparse_bwd_src_kernel<T, VEC, LP><<<g.blocks, 256, 0, st>>>(a, dvo, q, k, attn, dx, d_v, d_k, scale);        \
+		L1B_LAUNCH_CHECK();                                                                                       \
+	} while (0)
+	if (VEC > 1 && a.lph == 4)
+		L1B_BWD(4);
+	else if (VEC > 1 && a.lph == 8)
+		L1B_BWD(8);
+	else if (VEC > 1 && a.lph == 16)
+		L1B_BWD(16);
+	else if (VEC > 1 && a.lph == 32)
+		L1B_BWD(32);
+	else
+		L1B_BWD(0);
+#undef L1B_BWD
 	return L1ATTN_OK;
 }
 
