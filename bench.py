@@ -200,8 +200,10 @@ def metric_name(kind):
 
 def config_of(args, wl):
     bs, n, h, w = wl["shape"]
-    c = {"workload": "%s: %s" % (args.workload, "x".join(map(str, wl["shape"]))), "per_gpu_batch": bs,
-         "global_batch": bs * args.gpus, "n_tok": n, "heads": h, "width": w,
+    strong = getattr(args, "scaling", "weak") == "strong"
+    c = {"workload": "%s: %s" % (args.workload, "x".join(map(str, wl["shape"]))),
+         "per_gpu_batch": bs / args.gpus if strong else bs,
+         "global_batch": bs if strong else bs * args.gpus, "n_tok": n, "heads": h, "width": w,
          "partition": "independent batch items per GPU, no collective",
          "l2": "per-step working set (>= 2 GiB dense, 0.8 GB sparse) exceeds the 126 MB L2; no flush"}
     if wl["kind"] == "sparse":
@@ -260,7 +262,13 @@ def run_ours(args, wl):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     cabi.lib()
+    import l1attn_shard as shard
     kind, shape = wl["kind"], wl["shape"]
+    if args.scaling == "strong":  # the workload's batch items are dealt out to the ranks
+        lo, hi = shard.shard_range(shape[0], rank, world)
+        if hi == lo:
+            raise SystemExit("bench.py: more ranks than batch items in --scaling strong")
+        shape = (hi - lo,) + tuple(shape[1:])
     bs, n, h, w = shape
     gen = torch.Generator(device=dev).manual_seed(2000 + rank)
     pk = peaks()
@@ -328,12 +336,14 @@ def run_ours(args, wl):
     total_ms = ev[0][0].elapsed_time(ev[-1][2])
     fwd_ms = sum(e[0].elapsed_time(e[1]) for e in ev) / args.steps
     bwd_ms = sum(e[1].elapsed_time(e[2]) for e in ev) / args.steps
-    t = torch.tensor([total_ms], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    total_ms = float(t.item())
+    total_ms = shard.max_over_ranks(total_ms, dev)
     ms_per_step = total_ms / args.steps
-    value = units * world / (ms_per_step * 1e-3) / 1e9
+    all_units = units
+    if world > 1:  # units of every rank (ranks may hold different batch counts under strong scaling)
+        tu = torch.tensor([units], device=dev, dtype=torch.float64)
+        dist.all_reduce(tu)
+        all_units = float(tu.item())
+    value = all_units / (ms_per_step * 1e-3) / 1e9
 
     # ---- end to end through the host-buffer C ABI (rank-local; max over ranks)
     e2e_steps = max(1, min(args.steps, 3))
@@ -371,11 +381,8 @@ def run_ours(args, wl):
         e2e_step()
     torch.cuda.synchronize()
     e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
-    t = torch.tensor([e2e_ms], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    e2e_ms = float(t.item())
-    e2e_value = units * world / (e2e_ms * 1e-3) / 1e9
+    e2e_ms = shard.max_over_ranks(e2e_ms, dev)
+    e2e_value = all_units / (e2e_ms * 1e-3) / 1e9
     # clock samples over both timed regions (device-resident steps and end-to-end steps)
     clocks = sampler.window(t_wall0, time.time()) if sampler else None
 
@@ -416,7 +423,7 @@ def run_ours(args, wl):
             cpu = dict(value=r, unit=unit, cores=info["cores"], kind=info["kind"], sample=info["sample"])
         line = {
             "metric": metric_name(kind), "value": value, "unit": unit, "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": args.scaling,
             "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config_of(args, wl),
             "fwd_ms": fwd_ms, "bwd_ms": bwd_ms, "roofline": roof, "alu_roofline": alu, "cpu_baseline": cpu,
             "e2e": {"value": e2e_value, "unit": unit, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
@@ -442,6 +449,9 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--compare-reference-cuda", action="store_true",
                     help="also time the reference's own GPU kernels (oracle/_ref, rebuilt for sm_100) on the same inputs")
+    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
+                    help="weak (default): every rank runs the full workload on its own data; strong: the "
+                         "workload's batch is split across the ranks")
     ap.add_argument("--kernel-only", action="store_true", help="skip the end-to-end and CPU legs (profiling runs)")
     args = ap.parse_args()
     wl = WORKLOADS[args.workload]
