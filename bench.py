@@ -286,7 +286,7 @@ def run_ours(args, wl):
             cabi.dense_fwd(q, k, out=attn)
 
         bwd_scratch = torch.empty(cabi.lib().l1attn_dense_bwd_scratch_bytes(bs, n, h, w, 0), dtype=torch.uint8, device=dev)
-        launches_per_step = 4  # forward; tie detector + one kernel per gradient
+        launches_per_step = 3  # forward; tie detector; backward (both gradients in one launch)
 
         def bwd():
             cabi.dense_bwd(g, q, k, out=(dq, dk), scratch=bwd_scratch)

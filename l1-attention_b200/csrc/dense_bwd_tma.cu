@@ -20,7 +20,7 @@
 // Exact ties between random floats occur ~1.5e-8 per term (a few hundred per call at 16x1024x16x64),
 // zero-padded tokens tie everywhere; both cases stay exact and cost the exact loop only where they occur.
 //
-// Structure: one persistent launch per pass, one CTA per SM, work item = (batch, 8 heads, 32 x-rows,
+// Structure: one persistent launch for both passes, one CTA per SM, work item = (batch, 8 heads, 32 x-rows,
 // all 64 width columns of a 64-wide slice).  One thread streams y in tiles of 16 through a 4-stage
 // ring of TMA tensor loads (no multicast): the b rows as two [y][head][32 w] boxes with the 128-byte
 // swizzle, and the G tile as a [.][.][8 heads] box of the heads-innermost gradient tensor -- 32-byte
@@ -30,6 +30,7 @@
 // (8 warps with 8 x 8 tiles measured half the speed: with two warps per scheduler the
 // compare -> predicated-add latency was exposed, "wait" stalls of ~5 cycles per instruction.)
 // All mbarrier waits are bounded (tma.cuh).
+#include <type_traits>
 #include "common.cuh"
 #include "tma.cuh"
 #include "dense_bwd_tiles.h"
@@ -141,13 +142,15 @@ struct Feeder {
 	int dead;
 };
 
-// PASS 0: d_q (a = q, b = k, x = t, y = s).  PASS 1: d_k (a = k, b = q, x = s, y = t).
-template <int PASS>
+// Work items [0, per_pass) are pass 0: d_q (a = q, b = k, x = t, y = s); items [per_pass, 2 per_pass) are
+// pass 1: d_k (a = k, b = q, x = s, y = t).  One launch walks both, so the last wave of CTAs is as
+// full as the item count allows; the per-item code is compiled once per pass (generic lambda).
 __global__ void __launch_bounds__(NTHREADS, 1)
-dense_bwd_tma_kernel(const __grid_constant__ CUtensorMap bmap, const __grid_constant__ CUtensorMap gmap,
-		     const float *__restrict__ av_base, float *__restrict__ out_base,
-		     const unsigned char *__restrict__ flags, BwdFlagLayout fl, int n_tok, int n_heads, int width,
-		     float scale, BwdWork wk, int *err)
+dense_bwd_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kmap,
+		     const __grid_constant__ CUtensorMap gmap0, const __grid_constant__ CUtensorMap gmap1,
+		     const float *__restrict__ q, const float *__restrict__ k, float *__restrict__ d_q,
+		     float *__restrict__ d_k, const unsigned char *__restrict__ flags, BwdFlagLayout fl, int n_tok,
+		     int n_heads, int width, float scale, BwdWork wk, int *err)
 {
 	extern __shared__ __align__(1024) unsigned char smem_raw[];
 	// 1024-byte alignment by OFFSET into the shared array: a pointer rebuilt from an integer loses its
@@ -174,23 +177,25 @@ dense_bwd_tma_kernel(const __grid_constant__ CUtensorMap bmap, const __grid_cons
 	// Thread 0 keeps the ring NSTAGE-2 tiles ahead of the math: before each y tile it refills the
 	// stage that every warp released two tiles ago, so it never waits for a straggler.
 	auto issue_one = [&]() {
-		if (fd.item >= wk.per_pass || fd.dead)
+		if (fd.item >= wk.total || fd.dead)
 			return;
 		const int st = fd.st;
 		if (!mbar_wait(&empty_bar[st], fd.ph, err)) {
 			fd.dead = 1;
 			return;
 		}
-		const BwdItem x = decode(wk, fd.item);
+		const bool pass1 = fd.item >= wk.per_pass;
+		const BwdItem x = decode(wk, pass1 ? fd.item - wk.per_pass : fd.item);
+		const CUtensorMap *bm = pass1 ? &qmap : &kmap;
 		unsigned char *dst = stages + size_t(st) * STAGE_BYTES;
 		const int y0 = fd.yt * TY;
 		mbar_expect_tx(&full_bar[st], STAGE_BYTES);
-		tma_load_4d(dst, &bmap, &full_bar[st], x.w0, x.h0, y0, x.b);
-		tma_load_4d(dst + B_BYTES, &bmap, &full_bar[st], x.w0 + 32, x.h0, y0, x.b);
-		if (PASS == 0) // box {8 h, TX t, TY s}
-			tma_load_4d(dst + 2 * B_BYTES, &gmap, &full_bar[st], x.h0, x.x0, y0, x.b);
+		tma_load_4d(dst, bm, &full_bar[st], x.w0, x.h0, y0, x.b);
+		tma_load_4d(dst + B_BYTES, bm, &full_bar[st], x.w0 + 32, x.h0, y0, x.b);
+		if (!pass1) // box {8 h, TX t, TY s}
+			tma_load_4d(dst + 2 * B_BYTES, &gmap0, &full_bar[st], x.h0, x.x0, y0, x.b);
 		else // box {8 h, TY t, TX s}
-			tma_load_4d(dst + 2 * B_BYTES, &gmap, &full_bar[st], x.h0, y0, x.x0, x.b);
+			tma_load_4d(dst + 2 * B_BYTES, &gmap1, &full_bar[st], x.h0, y0, x.x0, x.b);
 		if (st + 1 == NSTAGE) {
 			fd.st = 0;
 			fd.ph ^= 1;
@@ -212,7 +217,10 @@ dense_bwd_tma_kernel(const __grid_constant__ CUtensorMap bmap, const __grid_cons
 	int st = 0;
 	uint32_t ph = 0;
 	int dead = 0;
-	for (unsigned item = blockIdx.x; item < wk.per_pass; item += gridDim.x) {
+	auto run_item = [&](auto pass_tag, unsigned item) {
+		constexpr int PASS = decltype(pass_tag)::value;
+		const float *av_base = PASS == 0 ? q : k;
+		float *out_base = PASS == 0 ? d_q : d_k;
 		float a[XR][8], acc[XR][8], rs[XR] = {0.f, 0.f, 0.f, 0.f};
 		{
 			const BwdItem x = decode(wk, item);
@@ -284,6 +292,12 @@ dense_bwd_tma_kernel(const __grid_constant__ CUtensorMap bmap, const __grid_cons
 				}
 			}
 		}
+	};
+	for (unsigned item = blockIdx.x; item < wk.total; item += gridDim.x) {
+		if (item < wk.per_pass)
+			run_item(std::integral_constant<int, 0>{}, item);
+		else
+			run_item(std::integral_constant<int, 1>{}, item - wk.per_pass);
 	}
 }
 
@@ -330,18 +344,14 @@ int dense_bwd_tma_launch(const void *d_attn, const void *q, const void *k, void 
 	int dev = 0, sms = 0;
 	L1B_CUDA(cudaGetDevice(&dev));
 	L1B_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-	const unsigned grid = wk.per_pass < unsigned(sms) ? wk.per_pass : unsigned(sms);
+	const unsigned grid = wk.total < unsigned(sms) ? wk.total : unsigned(sms);
 	const size_t smem = size_t(NSTAGE) * STAGE_BYTES + 1024;
-	L1B_CUDA(cudaFuncSetAttribute(dense_bwd_tma_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
-	L1B_CUDA(cudaFuncSetAttribute(dense_bwd_tma_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+	L1B_CUDA(cudaFuncSetAttribute(dense_bwd_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
 	const float scale = float(-1.0 / sqrt(double(width)));
 	const BwdFlagLayout fl = bwd_flag_layout(bs, n_tok, n_heads, width);
-	// pass 0: d_q from (a = q, b = k);  pass 1: d_k from (a = k, b = q); one launch each, same stream
-	dense_bwd_tma_kernel<0><<<grid, NTHREADS, smem, st>>>(kmap, gmap0, (const float *)q, (float *)d_q, flags, fl, n_tok,
-							       n_heads, width, scale, wk, err);
-	L1B_LAUNCH_CHECK();
-	dense_bwd_tma_kernel<1><<<grid, NTHREADS, smem, st>>>(qmap, gmap1, (const float *)k, (float *)d_k, flags, fl, n_tok,
-							       n_heads, width, scale, wk, err);
+	dense_bwd_tma_kernel<<<grid, NTHREADS, smem, st>>>(qmap, kmap, gmap0, gmap1, (const float *)q, (const float *)k,
+							    (float *)d_q, (float *)d_k, flags, fl, n_tok, n_heads, width, scale,
+							    wk, err);
 	L1B_LAUNCH_CHECK();
 	return L1ATTN_OK;
 }

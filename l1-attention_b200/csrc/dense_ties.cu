@@ -8,8 +8,8 @@
 //
 // Exact, in two steps.  One CTA handles NC width columns of one (batch, head):
 //   1. filter: every k value sets two bits (two hash functions) of its column's bitmap in shared
-//      memory; a q value whose two bits are both set is a candidate.  With >= 128 bits per token the
-//      false-candidate rate is ~1/4096 per value, so tie-free data yields about one candidate per CTA;
+//      memory; a q value whose two bits are both set is a candidate.  With 128 bits per token (up to
+//      2048 tokens) the false-candidate rate is ~1/4096 per value: about one candidate per CTA;
 //   2. proof: every candidate value is compared, bit pattern against bit pattern, with all k values
 //      of its column (held in registers by the threads that loaded them).  Matching k rows and
 //      the candidate's q row are the rows that tie.
@@ -23,7 +23,7 @@
 namespace l1b {
 namespace {
 
-constexpr int NT = 256;
+constexpr int NT_MAX = 1024; // threads per CTA: 256..1024, chosen so that one batch of TB tokens per thread covers n_tok when possible
 constexpr int TB = 4;    // tokens per thread per batch
 constexpr int CAP = 512; // candidate list entries per CTA
 
@@ -34,6 +34,7 @@ __device__ __forceinline__ unsigned hash2(unsigned b, int sh) { return ((b ^ (b 
 template <int NC>
 __device__ __forceinline__ void load_batch(const float *base, size_t row, int t0, int n_tok, int ncol, float (&v)[TB][NC])
 {
+	const int NT = blockDim.x;
 #pragma unroll
 	for (int i = 0; i < TB; i++) {
 		const int t = t0 + i * NT;
@@ -55,7 +56,7 @@ __device__ __forceinline__ void load_batch(const float *base, size_t row, int t0
 
 // grid: bs * n_heads * ceil(width / NC) CTAs.  smem: NC bitmaps of (1 << log2bits) bits.
 template <int NC>
-__global__ void __launch_bounds__(NT) dense_ties_kernel(const float *__restrict__ q, const float *__restrict__ k,
+__global__ void __launch_bounds__(NT_MAX) dense_ties_kernel(const float *__restrict__ q, const float *__restrict__ k,
 							 unsigned char *flags, int n_tok, int n_heads, int width,
 							 int log2bits, BwdFlagLayout fl)
 {
@@ -64,6 +65,7 @@ __global__ void __launch_bounds__(NT) dense_ties_kernel(const float *__restrict_
 	__shared__ unsigned cand_where[CAP]; // (column << 24) | q token
 	__shared__ unsigned char cand_hit[CAP];
 	__shared__ int n_cand, overflow;
+	const int NT = blockDim.x;
 	const unsigned words = 1u << (log2bits - 5);
 	const int sh = 32 - log2bits;
 	const int ncg = (width + NC - 1) / NC;
@@ -199,7 +201,10 @@ int launch_nc(const float *q, const float *k, unsigned char *flags, int bs, int 
 		return 1;
 	const size_t smem = size_t(NC) * (size_t(1) << log2bits) / 8;
 	L1B_CUDA(cudaFuncSetAttribute(dense_ties_kernel<NC>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
-	dense_ties_kernel<NC><<<unsigned(grid), NT, smem, st>>>(q, k, flags, n_tok, n_heads, width, log2bits, fl);
+	int nt = 256;
+	while (nt < NT_MAX && nt * TB < n_tok)
+		nt *= 2;
+	dense_ties_kernel<NC><<<unsigned(grid), nt, smem, st>>>(q, k, flags, n_tok, n_heads, width, log2bits, fl);
 	L1B_LAUNCH_CHECK();
 	return L1ATTN_OK;
 }
@@ -214,17 +219,15 @@ int dense_ties_launch(const float *q, const float *k, unsigned char *flags, int 
 {
 	if (width % 4 != 0 || n_tok >= (1 << 24))
 		return 1;
-	int log2bits = 15; // >= 128 bits per token, between 4 KiB and 64 KiB per column
-	while (log2bits < 19 && (1 << log2bits) < 128 * n_tok)
+	// 128 bits per token while four columns fit in 128 KiB of shared memory (n_tok <= 2048), fewer
+	// beyond: more false candidates to prove, and past ~16k tokens the list overflows into the
+	// conservative marking.  Four columns per CTA keep the global loads 16 bytes wide.
+	int log2bits = 15;
+	while (log2bits < 18 && (1 << log2bits) < 128 * n_tok)
 		log2bits++;
-	const size_t per_col = (size_t(1) << log2bits) / 8;
 	const BwdFlagLayout fl = bwd_flag_layout(bs, n_tok, n_heads, width);
 	L1B_CUDA(cudaMemsetAsync(flags, 0, fl.bytes(), st));
-	if (4 * per_col <= 96 * 1024)
-		return launch_nc<4>(q, k, flags, bs, n_tok, n_heads, width, log2bits, fl, st);
-	if (2 * per_col <= 96 * 1024)
-		return launch_nc<2>(q, k, flags, bs, n_tok, n_heads, width, log2bits, fl, st);
-	return launch_nc<1>(q, k, flags, bs, n_tok, n_heads, width, log2bits, fl, st);
+	return launch_nc<4>(q, k, flags, bs, n_tok, n_heads, width, log2bits, fl, st);
 }
 
 } // namespace l1b
