@@ -393,14 +393,15 @@ def run_ours(args, wl):
     if rank == 0:
         unit = "Gop/s" if kind == "dense" else "Gedge-inst/s"
         if kind == "dense":
-            # dominant kernel: one backward pass (two launches of the same kernel, one per gradient, ~equal
-            # durations; their CUDA-event time bwd_ms also holds the ~0.1 ms tie detector, so bwd_ms/2 is a
-            # slight over-estimate of one launch).  HBM algorithmic bytes per launch: read d_attn once,
-            # read q and k, write one gradient.
-            alg_bytes = 4.0 * (bs * n * n * h + 3 * bs * n * h * w)
-            roof = {"bound": "hbm", "kernel": "dense_bwd_tma_kernel (one of two launches per step)",
-                    "achieved": alg_bytes / (0.5 * bwd_ms * 1e-3) / 1e9,
-                    "peak": pk["hbm_gbs"], "unit": "GB/s", "traffic": None, "peak_source": pk["source"],
+            # dominant kernel: the backward launch (both gradient passes; its CUDA-event time bwd_ms also
+            # holds the ~0.1 ms tie detector).  HBM algorithmic bytes per launch: d_attn read once per pass,
+            # q and k read per pass, both gradients written.
+            alg_bytes = 4.0 * (2 * bs * n * n * h + 6 * bs * n * h * w)
+            roof = {"bound": "hbm", "kernel": "dense_bwd_tma_kernel",
+                    "achieved": alg_bytes / (bwd_ms * 1e-3) / 1e9,
+                    "peak": pk["hbm_gbs"], "unit": "GB/s", "peak_source": pk["source"],
+                    # ncu dram__bytes_read+write of this kernel at B=2,T=1024,H=16,W=64 (profiles/), scaled by batch
+                    "traffic": (311.8e6 * bs / 2.0) if (n, h, w) == (1024, 16, 64) else None,
                     "note": "the kernel is FP32/ALU-pipe bound, not HBM bound: see alu_roofline"}
             roof["frac"] = roof["achieved"] / roof["peak"]
             mhz = (clocks or {}).get("sm_max_mhz") or pk["sm_max_mhz"]
