@@ -57,3 +57,29 @@ def expandCoo(co):
     (cuda/l1attn_sparse_cuda.py:58-101), computed by a GPU kernel.
     """
     return l1attn_sparse_cuda_drv.expand_coo(torch.as_tensor(co))
+
+
+class SparseGraph:
+    """One graph, preprocessed once and reused by every layer and step (not in the reference, whose
+    callers redo `expandCoo(co)` + `.to(device)` by hand and whose kernels need no index).
+
+    `co` is the [n_edges, 2] list of (dst, src) pairs.  Construction runs expandCoo on the GPU and keeps
+    the expanded list on `device`; the kernels' edge index is built on first use and cached by the
+    driver for as long as this object keeps the list alive.
+
+        g = SparseGraph(co, device="cuda")
+        vo = g.attend(v, q, k)                      # L1AttnSparse
+        vo = g.attend_bidi(vf, vb, q, k)            # L1AttnSparseBidi
+    """
+
+    def __init__(self, co, device="cuda"):
+        co = torch.as_tensor(co).to(device)
+        self.coo, self.dst_mxlen, self.src_mxlen = expandCoo(co)
+        self.n_edges = int(self.coo.shape[0])
+
+    def attend(self, v, q, k, use_softmax=True):
+        return L1AttnSparseFn.apply(v, q, k, self.coo, self.dst_mxlen, use_softmax)
+
+    def attend_bidi(self, vf, vb, q, k, use_softmax=True):
+        import l1attn_sparse_bidi_cuda
+        return l1attn_sparse_bidi_cuda.L1AttnSparseBidiFn.apply(vf, vb, q, k, self.coo, self.dst_mxlen, use_softmax)

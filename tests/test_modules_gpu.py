@@ -103,6 +103,27 @@ def test_sparse_five_argument_call_defaults_to_softmax():
     assert t[0].grad is not None
 
 
+def test_sparse_graph_object_reused_across_layers():
+    """SparseGraph: expandCoo + device placement once, same results as the module calls."""
+    from oracle import oracle
+    import l1attn_sparse_cuda
+    co = torch.stack([torch.randint(0, 20, (150,)), torch.randint(0, 20, (150,))], 1)
+    g = l1attn_sparse_cuda.SparseGraph(co)
+    rcoo, rdm, rsm = oracle.expand_coo(co.numpy())
+    assert g.coo.is_cuda and np.array_equal(g.coo.cpu().numpy(), rcoo) and (g.dst_mxlen, g.src_mxlen) == (rdm, rsm)
+    x = torch.randn(2, 20, 4, 32, device="cuda")
+    for _ in range(3):  # "layers": the edge index is built once and reused
+        t = [torch.randn(2, 20, 4, 32, device="cuda", requires_grad=True) for _ in range(4)]
+        vo = g.attend(t[0], t[2], t[3])
+        ref, _ = oracle.sparse_fwd(*(a.detach().cpu().double().numpy() for a in (t[0], t[2], t[3])), rcoo, rdm, True)
+        assert_close(vo.detach().cpu().numpy(), ref, 1e-5)
+        bvo = g.attend_bidi(t[0], t[1], t[2], t[3])
+        bref, _ = oracle.sparse_bidi_fwd(*(a.detach().cpu().double().numpy() for a in t), rcoo, rdm, True)
+        assert_close(bvo.detach().cpu().numpy(), bref, 1e-5)
+        (vo * x).sum().backward()
+        assert all(a.grad is not None for a in (t[0], t[2], t[3]))
+
+
 def test_sparse_driver_errors():
     import l1attn_sparse_cuda_drv as drv
     q = torch.randn(1, 3, 2, 8, device="cuda")
