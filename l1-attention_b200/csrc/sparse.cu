@@ -78,8 +78,12 @@ template <int LPHC> __device__ __forceinline__ bool decode(const SparseArgs &a, 
 // any of them is used, so U row fetches (L2 latency each) are in flight per warp instead of one.
 constexpr int U = 4;
 
+// Walk of this lane's vectors of a row: x = li*VEC, += lanes-per-head * VEC.  With NX > 0 the trip count
+// is a compile-time constant (width == NX * lanes-per-head * VEC) and the walk unrolls completely.
+#define L1B_XLOOP(WIDTH) _Pragma("unroll") for (int it_ = 0, x = w.li * VEC; (NX > 0 ? it_ < NX : x < (WIDTH)); it_++, x += step)
+
 // ---- forward, dst pass: scores -> exp -> (+1)-softmax -> attn, vo[dst] = sum_r a_r v[src_r] ----
-template <typename T, int VEC, int LPHC>
+template <typename T, int VEC, int LPHC, int NX>
 __global__ void __launch_bounds__(256) sparse_fwd_dst_kernel(SparseArgs a, const T *__restrict__ v,
 							      const T *__restrict__ q, const T *__restrict__ k,
 							      T *__restrict__ vo, T *attn, T scale)
@@ -105,7 +109,7 @@ __global__ void __launch_bounds__(256) sparse_fwd_dst_kernel(SparseArgs a, const
 			src[u] = r0 + u < dm ? slots[r0 + u] : -1;
 			part[u] = T(0);
 		}
-		for (int x = w.li * VEC; x < W; x += step) {
+		L1B_XLOOP(W) {
 			const Pack<T, VEC> qv = ldv<T, VEC>(qrow + x, w.head_ok);
 			Pack<T, VEC> kv[U];
 #pragma unroll
@@ -136,7 +140,7 @@ __global__ void __launch_bounds__(256) sparse_fwd_dst_kernel(SparseArgs a, const
 	__syncwarp();
 
 	T *orow = vo + ((tokrow + dst) * H + hh) * Wv;
-	for (int x = w.li * VEC; x < Wv; x += step) {
+	L1B_XLOOP(Wv) {
 		Pack<T, VEC> acc = ldv<T, VEC>(nullptr, false);
 		for (int r0 = 0; r0 < dm; r0 += U) {
 			T ar[U];
@@ -160,7 +164,7 @@ __global__ void __launch_bounds__(256) sparse_fwd_dst_kernel(SparseArgs a, const
 }
 
 // ---- forward, src pass (bidi only): vo[src] += sum_{incoming (dst,r)} a[dst][r] * vb[dst] ----
-template <typename T, int VEC, int LPHC>
+template <typename T, int VEC, int LPHC, int NX>
 __global__ void __launch_bounds__(256) sparse_fwd_src_kernel(SparseArgs a, const T *__restrict__ vb,
 							      const T *__restrict__ attn, T *vo)
 {
@@ -175,7 +179,7 @@ __global__ void __launch_bounds__(256) sparse_fwd_src_kernel(SparseArgs a, const
 	const int lph = LPHC > 0 ? LPHC : a.lph;
 	const int step = lph * VEC;
 	T *orow = vo + ((tokrow + src) * H + w.h) * Wv;
-	for (int x = w.li * VEC; x < Wv; x += step) {
+	L1B_XLOOP(Wv) {
 		Pack<T, VEC> acc = ldv<T, VEC>(nullptr, false);
 		for (int eb = e0; eb < e1; eb += U) {
 			T ar[U];
@@ -206,7 +210,7 @@ __global__ void __launch_bounds__(256) sparse_fwd_src_kernel(SparseArgs a, const
 //   softmax: dx_r = a_r (ds_r - sum_j a_j ds_j)   [same as the reference's Jacobian product,
 //            cuda/l1attn_sparse_cuda_kernel.cu:256-295, without its O(dst_mxlen^2) loop]
 //   else:    dx_r = a_r ds_r
-template <typename T, int VEC, int LPHC>
+template <typename T, int VEC, int LPHC, int NX>
 __global__ void __launch_bounds__(256) sparse_bwd_dst_kernel(SparseArgs a, const T *__restrict__ dvo,
 							      const T *__restrict__ v, const T *__restrict__ vb,
 							      const T *__restrict__ q, const T *__restrict__ k,
@@ -237,7 +241,7 @@ __global__ void __launch_bounds__(256) sparse_bwd_dst_kernel(SparseArgs a, const
 			src[u] = r0 + u < dm ? slots[r0 + u] : -1;
 			part[u] = T(0);
 		}
-		for (int x = w.li * VEC; x < Wv; x += step) {
+		L1B_XLOOP(Wv) {
 			const Pack<T, VEC> gv = ldv<T, VEC>(gdst + x, w.head_ok);
 			Pack<T, VEC> vv[U], gs[U];
 #pragma unroll
@@ -286,7 +290,7 @@ __global__ void __launch_bounds__(256) sparse_bwd_dst_kernel(SparseArgs a, const
 
 	const T *qrow = q + ((tokrow + dst) * H + hh) * W;
 	T *orow = d_q + ((tokrow + dst) * H + hh) * W;
-	for (int x = w.li * VEC; x < W; x += step) {
+	L1B_XLOOP(W) {
 		const Pack<T, VEC> qv = ldv<T, VEC>(qrow + x, w.head_ok);
 		Pack<T, VEC> acc = ldv<T, VEC>(nullptr, false);
 		for (int r0 = 0; r0 < dm; r0 += U) {
@@ -315,7 +319,7 @@ __global__ void __launch_bounds__(256) sparse_bwd_dst_kernel(SparseArgs a, const
 	}
 	if (a.bidi) { // d_vb[dst] = sum_r a_r dvo[src_r]
 		T *brow = d_vb + ((tokrow + dst) * H + hh) * Wv;
-		for (int x = w.li * VEC; x < Wv; x += step) {
+		L1B_XLOOP(Wv) {
 			Pack<T, VEC> acc = ldv<T, VEC>(nullptr, false);
 			for (int r0 = 0; r0 < dm; r0 += U) {
 				T ar[U];
@@ -340,7 +344,7 @@ __global__ void __launch_bounds__(256) sparse_bwd_dst_kernel(SparseArgs a, const
 }
 
 // ---- backward, src pass: d_v[src] = sum a dvo[dst];  d_k[src] = -scale sum sign(q[dst]-k[src]) dx ----
-template <typename T, int VEC, int LPHC>
+template <typename T, int VEC, int LPHC, int NX>
 __global__ void __launch_bounds__(256) sparse_bwd_src_kernel(SparseArgs a, const T *__restrict__ dvo,
 							      const T *__restrict__ q, const T *__restrict__ k,
 							      const T *__restrict__ attn, const T *__restrict__ dx,
@@ -357,7 +361,7 @@ __global__ void __launch_bounds__(256) sparse_bwd_src_kernel(SparseArgs a, const
 	const int lph = LPHC > 0 ? LPHC : a.lph;
 	const int step = lph * VEC;
 	T *vrow = d_v + ((tokrow + src) * H + w.h) * Wv;
-	for (int x = w.li * VEC; x < Wv; x += step) {
+	L1B_XLOOP(Wv) {
 		Pack<T, VEC> acc = ldv<T, VEC>(nullptr, false);
 		for (int eb = e0; eb < e1; eb += U) {
 			T ar[U];
@@ -379,7 +383,7 @@ __global__ void __launch_bounds__(256) sparse_bwd_src_kernel(SparseArgs a, const
 	}
 	const T *krow = k + ((tokrow + src) * H + w.h) * W;
 	T *orow = d_k + ((tokrow + src) * H + w.h) * W;
-	for (int x = w.li * VEC; x < W; x += step) {
+	L1B_XLOOP(W) {
 		const Pack<T, VEC> kv = ldv<T, VEC>(krow + x, true);
 		Pack<T, VEC> acc = ldv<T, VEC>(nullptr, false);
 		for (int eb = e0; eb < e1; eb += U) {
@@ -438,25 +442,35 @@ int fwd_t(SparseArgs a, const T *v, const T *vb, const T *q, const T *k, T *vo, 
 		return L1ATTN_ERR_SHAPE;
 	const T scale = T(-1.0 / sqrt(double(a.width)));
 	// lanes per head as a compile-time constant for the common widths (16-byte vectors, 32..128+ columns)
-#define L1B_FWD(LP)                                                                                      \
+#define L1B_FWD(LP, NXV)                                                                                      \
 	do {                                                                                             \
-		sparse_fwd_dst_kernel<T, VEC, LP><<<g.blocks, 256, 0, st>>>(a, v, q, k, vo, attn, scale); \
+		sparse_fwd_dst_kernel<T, VEC, LP, NXV><<<g.blocks, 256, 0, st>>>(a, v, q, k, vo, attn, scale); \
 		L1B_LAUNCH_CHECK();                                                                      \
 		if (a.bidi) {                                                                            \
-			sparse_fwd_src_kernel<T, VEC, LP><<<g.blocks, 256, 0, st>>>(a, vb, attn, vo);     \
+			sparse_fwd_src_kernel<T, VEC, LP, NXV><<<g.blocks, 256, 0, st>>>(a, vb, attn, vo);     \
 			L1B_LAUNCH_CHECK();                                                              \
 		}                                                                                        \
 	} while (0)
-	if (VEC > 1 && a.lph == 4)
-		L1B_FWD(4);
+	// four vectors per lane exactly (width == v_width == 16 * lanes-per-head elements of 16-byte vectors): unrolled walk
+	const bool nx4 = VEC > 1 && a.width == a.v_width && a.width == 4 * a.lph * VEC;
+	if (nx4 && a.lph == 4)
+		L1B_FWD(4, 4);
+	else if (nx4 && a.lph == 8)
+		L1B_FWD(8, 4);
+	else if (nx4 && a.lph == 16)
+		L1B_FWD(16, 4);
+	else if (nx4 && a.lph == 32)
+		L1B_FWD(32, 4);
+	else if (VEC > 1 && a.lph == 4)
+		L1B_FWD(4, 0);
 	else if (VEC > 1 && a.lph == 8)
-		L1B_FWD(8);
+		L1B_FWD(8, 0);
 	else if (VEC > 1 && a.lph == 16)
-		L1B_FWD(16);
+		L1B_FWD(16, 0);
 	else if (VEC > 1 && a.lph == 32)
-		L1B_FWD(32);
+		L1B_FWD(32, 0);
 	else
-		L1B_FWD(0);
+		L1B_FWD(0, 0);
 #undef L1B_FWD
 	return L1ATTN_OK;
 }
@@ -473,23 +487,33 @@ int bwd_t(SparseArgs a, const T *dvo, const T *v, const T *vb, const T *q, const
 	if (!g.ok)
 		return L1ATTN_ERR_SHAPE;
 	const T scale = T(-1.0 / sqrt(double(a.width)));
-#define L1B_BWD(LP)                                                                                                       \
+#define L1B_BWD(LP, NXV)                                                                                                       \
 	do {                                                                                                              \
-		sparse_bwd_dst_kernel<T, VEC, LP><<<g.blocks, 256, 0, st>>>(a, dvo, v, vb, q, k, attn, dx, d_q, d_vb, scale); \
+		sparse_bwd_dst_kernel<T, VEC, LP, NXV><<<g.blocks, 256, 0, st>>>(a, dvo, v, vb, q, k, attn, dx, d_q, d_vb, scale); \
 		L1B_LAUNCH_CHECK();                                                                                       \
-		sparse_bwd_src_kernel<T, VEC, LP><<<g.blocks, 256, 0, st>>>(a, dvo, q, k, attn, dx, d_v, d_k, scale);        \
+		sparse_bwd_src_kernel<T, VEC, LP, NXV><<<g.blocks, 256, 0, st>>>(a, dvo, q, k, attn, dx, d_v, d_k, scale);        \
 		L1B_LAUNCH_CHECK();                                                                                       \
 	} while (0)
-	if (VEC > 1 && a.lph == 4)
-		L1B_BWD(4);
+	// four vectors per lane exactly (width == v_width == 16 * lanes-per-head elements of 16-byte vectors): unrolled walk
+	const bool nx4 = VEC > 1 && a.width == a.v_width && a.width == 4 * a.lph * VEC;
+	if (nx4 && a.lph == 4)
+		L1B_BWD(4, 4);
+	else if (nx4 && a.lph == 8)
+		L1B_BWD(8, 4);
+	else if (nx4 && a.lph == 16)
+		L1B_BWD(16, 4);
+	else if (nx4 && a.lph == 32)
+		L1B_BWD(32, 4);
+	else if (VEC > 1 && a.lph == 4)
+		L1B_BWD(4, 0);
 	else if (VEC > 1 && a.lph == 8)
-		L1B_BWD(8);
+		L1B_BWD(8, 0);
 	else if (VEC > 1 && a.lph == 16)
-		L1B_BWD(16);
+		L1B_BWD(16, 0);
 	else if (VEC > 1 && a.lph == 32)
-		L1B_BWD(32);
+		L1B_BWD(32, 0);
 	else
-		L1B_BWD(0);
+		L1B_BWD(0, 0);
 #undef L1B_BWD
 	return L1ATTN_OK;
 }
