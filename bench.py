@@ -42,6 +42,9 @@ WORKLOADS = {
     "dense_small": dict(kind="dense", shape=(2, 1024, 16, 64)),  # profiling size: 134 MB of scores, > L2
     "sparse_small": dict(kind="sparse", shape=(2, 4096, 8, 64), fan=31),
     "sparse_cfg4": dict(kind="sparse", shape=(8, 4096, 8, 64), fan=31),
+    # BASELINE config 5: training step of a 4-layer pre-LN transformer on L1AttnSparseBidi; not a model of
+    # the reference (it ships none for the sparse operator), written here from the config's description
+    "train_cfg5": dict(kind="train", batch=64, seq=256, d_model=256, heads=8, layers=4, vocab=64, fan=16),
 }
 SM_COUNT, FP32_LANES = 148, 128
 
@@ -243,6 +246,121 @@ def time_reference_cuda(kind, dev, v):
     out["speedup"] = (out["fwd_ms"] + out["bwd_ms"]) / (v["fwd_ms"] + v["bwd_ms"])
     out["note"] = "reference cuda/ extension rebuilt for sm_100 with its own flags, same tensors, CUDA events"
     return out
+
+
+# ----------------------------------------------------------------------------- config-5 training step
+
+def build_transformer(wl, attn_fn, dev):
+    """4-layer pre-LayerNorm transformer; attention = L1AttnSparseBidi over a fixed random graph.
+    attn_fn(vf, vb, q, k) -> vo, all [batch, seq, heads, width]."""
+    import torch
+    from torch import nn
+    d, hds, width = wl["d_model"], wl["heads"], wl["d_model"] // wl["heads"]
+
+    class Block(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.ln1, self.ln2 = nn.LayerNorm(d), nn.LayerNorm(d)
+            self.qkv = nn.Linear(d, 4 * d)  # q, k, vf, vb
+            self.wo = nn.Linear(d, d)
+            self.mlp = nn.Sequential(nn.Linear(d, 4 * d), nn.GELU(), nn.Linear(4 * d, d))
+
+        def forward(self, x):
+            b, t, _ = x.shape
+            q, k, vf, vb = (y.reshape(b, t, hds, width) for y in self.qkv(self.ln1(x)).chunk(4, -1))
+            x = x + self.wo(attn_fn(vf, vb, q, k).reshape(b, t, d))
+            return x + self.mlp(self.ln2(x))
+
+    class Model(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.tok, self.pos = nn.Embedding(wl["vocab"], d), nn.Parameter(torch.zeros(wl["seq"], d))
+            self.blocks = nn.ModuleList(Block() for _ in range(wl["layers"]))
+            self.ln, self.head = nn.LayerNorm(d), nn.Linear(d, wl["vocab"])
+
+        def forward(self, idx):
+            x = self.tok(idx) + self.pos
+            for blk in self.blocks:
+                x = blk(x)
+            return self.head(self.ln(x))
+
+    torch.manual_seed(5005)
+    return Model().to(dev)
+
+
+def run_train(args, wl):
+    import torch
+    import torch.nn.functional as F
+    import l1attn_sparse_cuda
+    import l1attn_sparse_bidi_cuda
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device -- this library has no CPU path")
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    n = wl["seq"]
+    co = bench_graph(n, wl["fan"], 5001)
+    graph = l1attn_sparse_cuda.SparseGraph(co, device=dev)
+    g = torch.Generator().manual_seed(5002)
+    tokens = torch.randint(0, wl["vocab"], (wl["batch"], n), generator=g).to(dev)
+    targets = torch.randint(0, wl["vocab"], (wl["batch"], n), generator=g).to(dev)
+
+    def timed(attn_fn, steps, warmup):
+        model = build_transformer(wl, attn_fn, dev)
+        opt = torch.optim.AdamW(model.parameters(), lr=1e-3)
+        losses = []
+
+        def step():
+            opt.zero_grad(set_to_none=True)
+            loss = F.cross_entropy(model(tokens).reshape(-1, wl["vocab"]), targets.reshape(-1))
+            loss.backward()
+            opt.step()
+            return loss
+
+        for _ in range(max(warmup, 3)):
+            losses.append(float(step()))
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            loss = step()
+        e1.record()
+        torch.cuda.synchronize()
+        losses.append(float(loss))
+        return e0.elapsed_time(e1) / steps, losses
+
+    ours = lambda vf, vb, q, k: graph.attend_bidi(vf, vb, q, k)
+    ms, losses = timed(ours, args.steps, args.warmup)
+    line = {"metric": "training tokens/s, 4-layer pre-LN transformer with L1AttnSparseBidi (config 5)",
+            "value": wl["batch"] * n / (ms * 1e-3), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "train_cfg5", **{k: v for k, v in wl.items() if k != "kind"},
+                       "edges": int(graph.n_edges), "dst_mxlen": int(graph.dst_mxlen), "optimizer": "AdamW"},
+            "loss_first": losses[0], "loss_last": losses[-1]}
+    if args.compare_reference_cuda:
+        refdir = os.path.join(ROOT, "oracle", "_ref")
+        if os.path.exists(os.path.join(refdir, "ref_l1attn_sparse_bidi_cuda_drv.so")):
+            sys.path.insert(0, refdir)
+            import ref_l1attn_sparse_bidi_cuda_drv as refdrv
+
+            class RefFn(torch.autograd.Function):  # the reference's autograd glue (cuda/l1attn_sparse_bidi_cuda.py:8-48)
+                @staticmethod
+                def forward(ctx, vf, vb, q, k):
+                    vf, vb, q, k = (t.contiguous() for t in (vf, vb, q, k))
+                    vo, attn = refdrv.forward(vf, vb, q, k, graph.coo, graph.dst_mxlen, True)
+                    ctx.save_for_backward(vf, vb, q, k, attn)
+                    return vo
+
+                @staticmethod
+                def backward(ctx, dvo):
+                    vf, vb, q, k, attn = ctx.saved_tensors
+                    return tuple(refdrv.backward(dvo.contiguous(), vf, vb, q, k, graph.coo, attn, graph.dst_mxlen, True))
+
+            rms, rl = timed(lambda vf, vb, q, k: RefFn.apply(vf, vb, q, k), args.steps, args.warmup)
+            line["reference_cuda"] = {"ms_per_step": rms, "tokens_per_s": wl["batch"] * n / (rms * 1e-3),
+                                      "speedup": rms / ms, "loss_last": rl[-1]}
+    print(json.dumps(line), flush=True)
 
 
 # ----------------------------------------------------------------------------- our arm
@@ -456,7 +574,13 @@ def main():
     ap.add_argument("--kernel-only", action="store_true", help="skip the end-to-end and CPU legs (profiling runs)")
     args = ap.parse_args()
     wl = WORKLOADS[args.workload]
-    if args.impl == "reference":
+    if wl["kind"] == "train":
+        if args.impl == "reference":
+            print(json.dumps({"impl": "reference", "unavailable": "the reference ships no model for config 5 and its CPU "
+                              "extension has no training loop; use --compare-reference-cuda on the default arm"}))
+        else:
+            run_train(args, wl)
+    elif args.impl == "reference":
         run_reference_arm(args, wl)
     else:
         run_ours(args, wl)

@@ -124,6 +124,45 @@ def test_sparse_graph_object_reused_across_layers():
         assert all(a.grad is not None for a in (t[0], t[2], t[3]))
 
 
+def test_training_steps_match_a_pure_torch_model():
+    """The config-5 style model (bench.build_transformer) trained for a few AdamW steps through
+    L1AttnSparseBidi must follow the same loss curve as the same model whose attention is a
+    differentiable pure-PyTorch restatement of the operator (scatter form of the reference math)."""
+    import math
+    import torch.nn.functional as F
+    import bench
+    import l1attn_sparse_cuda
+    wl = dict(kind="train", batch=4, seq=24, d_model=32, heads=4, layers=2, vocab=16, fan=5)
+    dev = torch.device("cuda")
+    graph = l1attn_sparse_cuda.SparseGraph(bench.bench_graph(wl["seq"], wl["fan"], 7), device=dev)
+    dst, src = graph.coo[:, 0].long(), graph.coo[:, 1].long()
+
+    def torch_bidi(vf, vb, q, k):
+        x = -(q[:, dst] - k[:, src]).abs().sum(-1) / math.sqrt(q.shape[-1])  # [b, edges, h]
+        e = torch.exp(x)
+        denom = torch.ones_like(q[..., 0]).index_add(1, dst, e)              # 1 + sum over the dst's edges
+        a = (e / denom[:, dst]).unsqueeze(-1)
+        return torch.zeros_like(vf).index_add(1, dst, a * vf[:, src]).index_add(1, src, a * vb[:, dst])
+
+    g = torch.Generator().manual_seed(1)
+    tokens = torch.randint(0, wl["vocab"], (wl["batch"], wl["seq"]), generator=g).to(dev)
+    targets = torch.randint(0, wl["vocab"], (wl["batch"], wl["seq"]), generator=g).to(dev)
+    curves = []
+    for attn in (lambda vf, vb, q, k: graph.attend_bidi(vf, vb, q, k), torch_bidi):
+        model = bench.build_transformer(wl, attn, dev)  # same seed inside: identical initial weights
+        opt = torch.optim.AdamW(model.parameters(), lr=3e-3)
+        losses = []
+        for _ in range(6):
+            opt.zero_grad()
+            loss = F.cross_entropy(model(tokens).reshape(-1, wl["vocab"]), targets.reshape(-1))
+            loss.backward()
+            opt.step()
+            losses.append(float(loss))
+        curves.append(losses)
+    assert curves[0][-1] < curves[0][0]
+    assert np.allclose(curves[0], curves[1], rtol=2e-4), curves
+
+
 def test_sparse_driver_errors():
     import l1attn_sparse_cuda_drv as drv
     q = torch.randn(1, 3, 2, 8, device="cuda")
