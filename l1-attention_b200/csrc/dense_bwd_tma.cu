@@ -133,15 +133,6 @@ __device__ __forceinline__ int opaque(int x)
 	return x;
 }
 
-// Feeding cursor of the TMA ring; lives in shared memory so that it costs the compute threads no
-// registers (only thread 0 touches it).
-struct Feeder {
-	unsigned item;
-	int yt, st;
-	uint32_t ph;
-	int dead;
-};
-
 // Work items [0, per_pass) are pass 0: d_q (a = q, b = k, x = t, y = s); items [per_pass, 2 per_pass) are
 // pass 1: d_k (a = k, b = q, x = s, y = t).  One launch walks both, so the last wave of CTAs is as
 // full as the item count allows; the per-item code is compiled once per pass (generic lambda).
@@ -157,7 +148,6 @@ dense_bwd_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_cons
 	// address space and every access through it becomes a generic load, which measured ~2x slower here
 	unsigned char *stages = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
 	__shared__ __align__(8) uint64_t full_bar[NSTAGE], empty_bar[NSTAGE];
-	__shared__ Feeder fd;
 
 	const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 	if (tid == 0) {
@@ -166,29 +156,31 @@ dense_bwd_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_cons
 			mbar_init(&empty_bar[s], NCW);
 		}
 		mbar_fence_init();
-		fd.item = blockIdx.x;
-		fd.yt = 0;
-		fd.st = 0;
-		fd.ph = 1;
-		fd.dead = 0;
 	}
 	__syncthreads();
 
-	// Thread 0 keeps the ring NSTAGE-2 tiles ahead of the math: before each y tile it refills the
-	// stage that every warp released two tiles ago, so it never waits for a straggler.
-	auto issue_one = [&]() {
-		if (fd.item >= wk.total || fd.dead)
-			return;
-		const int st = fd.st;
-		if (!mbar_wait(&empty_bar[st], fd.ph, err)) {
-			fd.dead = 1;
-			return;
+	// The ring runs NSTAGE-2 tiles ahead of the math.  The n-th tile this CTA consumes (n counts across
+	// work items) lives in stage n % NSTAGE.  While the warps work on tile n, ONE lane requests tile
+	// n + NSTAGE-2, whose stage every warp released two tiles ago, so the requester normally does not
+	// wait.  The duty rotates over the warps (tile n -> warp n % 16): a fixed issuing thread made its
+	// warp slower than the others, and the whole CTA ran at that warp's pace.
+	// issue_tile(it, yt, m): request y tile `yt` of work item `it` as ring entry m; yt may run past the
+	// item's last tile and then names a tile of the CTA's following items.
+	auto issue_tile = [&](unsigned it, int yt, unsigned m) -> bool {
+		while (yt >= wk.ny) {
+			yt -= wk.ny;
+			it += gridDim.x;
 		}
-		const bool pass1 = fd.item >= wk.per_pass;
-		const BwdItem x = decode(wk, pass1 ? fd.item - wk.per_pass : fd.item);
+		if (it >= wk.total)
+			return true;
+		const int st = int(m % NSTAGE);
+		if (!mbar_wait(&empty_bar[st], ((m / NSTAGE) & 1u) ^ 1u, err))
+			return false;
+		const bool pass1 = it >= wk.per_pass;
+		const BwdItem x = decode(wk, pass1 ? it - wk.per_pass : it);
 		const CUtensorMap *bm = pass1 ? &qmap : &kmap;
 		unsigned char *dst = stages + size_t(st) * STAGE_BYTES;
-		const int y0 = fd.yt * TY;
+		const int y0 = yt * TY;
 		mbar_expect_tx(&full_bar[st], STAGE_BYTES);
 		tma_load_4d(dst, bm, &full_bar[st], x.w0, x.h0, y0, x.b);
 		tma_load_4d(dst + B_BYTES, bm, &full_bar[st], x.w0 + 32, x.h0, y0, x.b);
@@ -196,26 +188,17 @@ dense_bwd_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_cons
 			tma_load_4d(dst + 2 * B_BYTES, &gmap0, &full_bar[st], x.h0, x.x0, y0, x.b);
 		else // box {8 h, TY t, TX s}
 			tma_load_4d(dst + 2 * B_BYTES, &gmap1, &full_bar[st], x.h0, y0, x.x0, x.b);
-		if (st + 1 == NSTAGE) {
-			fd.st = 0;
-			fd.ph ^= 1;
-		} else {
-			fd.st = st + 1;
-		}
-		if (++fd.yt == wk.ny) {
-			fd.yt = 0;
-			fd.item += gridDim.x;
-		}
+		return true;
 	};
 	if (tid == 0)
 		for (int i = 0; i < NSTAGE - 2; i++)
-			issue_one();
+			issue_tile(blockIdx.x, i, unsigned(i));
 
 	const int lh = lane & 7, lw = lane >> 3;
 	const int wx = warp & 7, wp = warp >> 3;
 	const int c = lw + 4 * wp; // 16-byte chunk (0..7) of each 32-wide half
-	int st = 0;
-	uint32_t ph = 0;
+	static_assert((NSTAGE & (NSTAGE - 1)) == 0, "stage index and parity are bit fields of the tile counter");
+	unsigned n = 0; // tiles consumed by this CTA so far
 	int dead = 0;
 	auto run_item = [&](auto pass_tag, unsigned item) {
 		constexpr int PASS = decltype(pass_tag)::value;
@@ -251,10 +234,12 @@ dense_bwd_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_cons
 		const unsigned char *yflags = flags == nullptr ? nullptr : flags + fl.yoff(PASS) + size_t(item / wk.nxt) * fl.ny;
 
 		for (int yt = 0; yt < wk.ny; yt++) {
-			if (opaque(tid) == 0)
-				issue_one();
+			if (opaque(tid) == int((n % NCW) * 32) && opaque(dead) == 0 &&
+			    !issue_tile(item + PASS * wk.per_pass, yt + NSTAGE - 2, n + NSTAGE - 2))
+				dead = 1;
 			__syncwarp();
-			if (opaque(dead) == 0 && !mbar_wait(&full_bar[st], ph, err))
+			const int st = int(n % NSTAGE);
+			if (opaque(dead) == 0 && !mbar_wait(&full_bar[st], (n / NSTAGE) & 1u, err))
 				dead = 1; // keep walking without waiting so the warps stay in step
 			const unsigned char *stage = stages + size_t(st) * STAGE_BYTES;
 			const bool exact = opaque(xflag) != 0 && (yflags == nullptr || yflags[yt] != 0); // yflags is read only for flagged x tiles
@@ -265,10 +250,7 @@ dense_bwd_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_cons
 			__syncwarp();
 			if (opaque(lane) == 0)
 				mbar_arrive(&empty_bar[st]);
-			if (++st == NSTAGE) {
-				st = 0;
-				ph ^= 1;
-			}
+			n++;
 		}
 
 		const BwdItem x = decode(wk, unsigned(opaque(int(item))));
