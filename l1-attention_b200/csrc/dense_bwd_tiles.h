@@ -9,21 +9,29 @@ constexpr int BWD_TX = 32; // x rows (tokens) per work item
 constexpr int BWD_WS = 64; // width columns per work item
 constexpr int BWD_TY = 16; // y rows (tokens of the other side) per pipeline stage
 
-// Tie flags, one byte each, for G = bs * head groups * width slices "groups":
-//   xflag[pass][G][nxt]  the x tile holds a row that ties with some row of the other side
+constexpr int BWD_XF = 4;  // x rows per x flag: the rows one warp of the backward owns
+constexpr int BWD_WF = 32; // width columns per flag group: the columns one warp of the backward owns,
+                           // i.e. those of a 64-wide slice with the same (w % 32) / 16
+
+// Tie flags, one byte each, for G = bs * head groups * width groups (two per width slice):
+//   xflag[pass][G][nxf]  rows [4i, 4i+4) of the x side hold a value that ties with some row of the other side
 //   yflag[pass][G][ny]   the y tile holds such a row of the other side
-// A (work item, y tile) pair needs the exact loop only if both its flags are set.
+// A warp of the backward (4 x rows, 8 heads, 32 width columns) needs the exact loop for a y tile only
+// if both flags are set.
 struct BwdFlagLayout {
-	size_t groups, nxt, ny;
-	__host__ __device__ size_t xoff(int pass) const { return size_t(pass) * groups * nxt; }
-	__host__ __device__ size_t yoff(int pass) const { return 2 * groups * nxt + size_t(pass) * groups * ny; }
-	__host__ __device__ size_t bytes() const { return 2 * groups * (nxt + ny); }
+	size_t groups, nxf, ny, nhg, nwf;
+	__host__ __device__ size_t group(int b, int h, int w) const { return (size_t(b) * nhg + size_t(h) / BWD_HG) * nwf + size_t(w) / BWD_WS * 2 + size_t(w) % 32 / 16; }
+	__host__ __device__ size_t xoff(int pass) const { return size_t(pass) * groups * nxf; }
+	__host__ __device__ size_t yoff(int pass) const { return 2 * groups * nxf + size_t(pass) * groups * ny; }
+	__host__ __device__ size_t bytes() const { return 2 * groups * (nxf + ny); }
 };
 inline BwdFlagLayout bwd_flag_layout(int bs, int n_tok, int n_heads, int width)
 {
 	BwdFlagLayout l;
-	l.groups = size_t(bs) * ((n_heads + BWD_HG - 1) / BWD_HG) * ((width + BWD_WS - 1) / BWD_WS);
-	l.nxt = (n_tok + BWD_TX - 1) / BWD_TX;
+	l.nhg = (n_heads + BWD_HG - 1) / BWD_HG;
+	l.nwf = size_t((width + BWD_WS - 1) / BWD_WS) * (BWD_WS / BWD_WF); // padded to whole width slices
+	l.groups = size_t(bs) * l.nhg * l.nwf;
+	l.nxf = size_t((n_tok + BWD_TX - 1) / BWD_TX) * (BWD_TX / BWD_XF); // padded to whole x tiles
 	l.ny = (n_tok + BWD_TY - 1) / BWD_TY;
 	return l;
 }

@@ -12,9 +12,9 @@
 // Two instructions per term.  With no ties (a != b) in a tile,
 //     sum_y sign(a-b) G = 2 * sum_y [a > b] G  -  sum_y G,
 // so the inner loop is one compare (FSETP) and one predicated add per term; the row sums
-// sum_y G(x,y,h) are a by-product (4 extra adds per 32 terms).  A (work item, y tile) pair may use
-// this form unless a detector kernel (dense_ties.cu) has found a token row in the x tile AND one in
-// the y tile that take part in a tie a == b (same batch, head, width index); such pairs run the
+// sum_y G(x,y,h) are a by-product (4 extra adds per 32 terms).  A warp (4 x rows, 8 heads, 32 width
+// columns) may use this form on a y tile unless a detector kernel (dense_ties.cu) has found a row among
+// its x rows AND one in the y tile that take part in a tie a == b (same batch, head group, width group); such pairs run the
 // exact loop (subtract, sign transfer, tie predicate, add) on halved G, so that one accumulator
 // serves both forms: out = scale * (2 acc - R), R summed over the compare-form tiles only.
 // Exact ties between random floats occur ~1.5e-8 per term (a few hundred per call at 16x1024x16x64),
@@ -44,6 +44,7 @@ constexpr int TY = BWD_TY; // y rows per stage (16)
 constexpr int WS = BWD_WS; // width slice per work item (64 = two 32-wide halves)
 constexpr int NCW = 16;  // warps: 8 x-groups of XR rows x 2 halves of the chunk range
 constexpr int XR = 4;    // x rows per thread
+static_assert(XR == BWD_XF && WS == 2 * BWD_WF, "a warp owns one x flag and one width group");
 constexpr int NSTAGE = 4;
 constexpr int B_BYTES = TY * HG * 32 * 4;  // one 32-wide half of the b tile: 16384
 constexpr int G_BYTES = TY * TX * HG * 4;  // 16384
@@ -230,8 +231,15 @@ dense_bwd_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_cons
 			}
 		}
 		// exact loop where a tile with a tying x row meets a tile with a tying y row (or always, without flags)
-		const int xflag = flags == nullptr ? 1 : int(flags[fl.xoff(PASS) + item]);
-		const unsigned char *yflags = flags == nullptr ? nullptr : flags + fl.yoff(PASS) + size_t(item / wk.nxt) * fl.ny;
+		// (this warp's 4 x rows and its 32 width columns; the flag arrays are padded to whole tiles and slices)
+		int xflag = 1;
+		const unsigned char *yflags = nullptr;
+		if (flags != nullptr) {
+			const BwdItem x = decode(wk, item);
+			const size_t g = fl.group(x.b, x.h0, x.w0 + wp * 16); // this warp's columns: (w % 32) / 16 == wp
+			xflag = int(flags[fl.xoff(PASS) + g * fl.nxf + size_t(x.x0 + wx * XR) / BWD_XF]);
+			yflags = flags + fl.yoff(PASS) + g * fl.ny;
+		}
 
 		for (int yt = 0; yt < wk.ny; yt++) {
 			if (opaque(tid) == int((n % NCW) * 32) && opaque(dead) == 0 &&

@@ -3,8 +3,8 @@
 // The two-instruction form of the backward (dense_bwd_tma.cu) is valid for a stretch of work only
 // if none of its `a` values equals a `b` value of the same (batch, head, width index): sign(0) must
 // be 0, and the compare form cannot see a tie.  This kernel finds every token row that takes part
-// in such a tie and marks the tiles that contain one (layout: dense_bwd_tiles.h); the backward
-// runs its exact loop where a marked x tile meets a marked y tile and the short loop elsewhere.
+// in such a tie and marks the row groups that contain one (layout: dense_bwd_tiles.h); a warp of the
+// backward runs its exact loop where its marked x rows meet a marked y tile and the short loop elsewhere.
 //
 // Exact, in two steps.  One CTA handles NC width columns of one (batch, head):
 //   1. filter: every k value sets two bits (two hash functions) of its column's bitmap in shared
@@ -90,9 +90,7 @@ __global__ void __launch_bounds__(NT_MAX) dense_ties_kernel(const float *__restr
 	const size_t row = size_t(n_heads) * width;
 	const float *qb = q + size_t(b) * n_tok * row + size_t(h) * width + w0;
 	const float *kb = k + size_t(b) * n_tok * row + size_t(h) * width + w0;
-	const unsigned nhg = (n_heads + BWD_HG - 1) / BWD_HG, nws = (width + BWD_WS - 1) / BWD_WS;
 	unsigned char *xq = flags + fl.xoff(0), *xk = flags + fl.xoff(1), *yk = flags + fl.yoff(0), *yq = flags + fl.yoff(1);
-	const size_t gbase = (size_t(b) * nhg + unsigned(h) / BWD_HG) * nws;
 	const bool one_batch = n_tok <= NT * TB;
 	float v[TB][NC];
 
@@ -133,8 +131,8 @@ __global__ void __launch_bounds__(NT_MAX) dense_ties_kernel(const float *__restr
 									cand_bits[idx] = bits;
 									cand_where[idx] = (unsigned(j) << 24) | unsigned(t);
 								} else { // list full: mark this q row without proof
-									const size_t g = gbase + unsigned(w0 + j) / BWD_WS;
-									xq[g * fl.nxt + t / BWD_TX] = 1;
+									const size_t g = fl.group(b, h, w0 + j);
+									xq[g * fl.nxf + t / BWD_XF] = 1;
 									yq[g * fl.ny + t / BWD_TY] = 1;
 									overflow = 1;
 								}
@@ -161,8 +159,8 @@ __global__ void __launch_bounds__(NT_MAX) dense_ties_kernel(const float *__restr
 #pragma unroll
 				for (int j = 0; j < NC; j++)
 					if (j == col && t < n_tok && v[i][j] == v[i][j] && canon(v[i][j]) == bits) {
-						const size_t g = gbase + unsigned(w0 + j) / BWD_WS;
-						xk[g * fl.nxt + t / BWD_TX] = 1; // k row t equals a q value
+						const size_t g = fl.group(b, h, w0 + j);
+						xk[g * fl.nxf + t / BWD_XF] = 1; // k row t equals a q value
 						yk[g * fl.ny + t / BWD_TY] = 1;
 						cand_hit[ci] = 1;
 					}
@@ -174,8 +172,8 @@ __global__ void __launch_bounds__(NT_MAX) dense_ties_kernel(const float *__restr
 				const int t = t0 + i * NT;
 				if (t < n_tok)
 					for (int j = 0; j < ncol; j++) {
-						const size_t g = gbase + unsigned(w0 + j) / BWD_WS;
-						xk[g * fl.nxt + t / BWD_TX] = 1;
+						const size_t g = fl.group(b, h, w0 + j);
+						xk[g * fl.nxf + t / BWD_XF] = 1;
 						yk[g * fl.ny + t / BWD_TY] = 1;
 					}
 			}
@@ -186,8 +184,8 @@ __global__ void __launch_bounds__(NT_MAX) dense_ties_kernel(const float *__restr
 		if (cand_hit[ci]) { // proven: this q row equals some k value
 			const unsigned wv = cand_where[ci];
 			const int t = int(wv & 0xffffffu), j = int(wv >> 24);
-			const size_t g = gbase + unsigned(w0 + j) / BWD_WS;
-			xq[g * fl.nxt + t / BWD_TX] = 1;
+			const size_t g = fl.group(b, h, w0 + j);
+			xq[g * fl.nxf + t / BWD_XF] = 1;
 			yq[g * fl.ny + t / BWD_TY] = 1;
 		}
 }
