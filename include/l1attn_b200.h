@@ -47,6 +47,11 @@ extern "C" {
 #define L1ATTN_F32 0
 #define L1ATTN_F64 1
 
+/* normalisation of l1attn_dense_softmax_v_fwd */
+#define L1ATTN_SV_SOFTMAX 0          /* softmax over the source tokens (F.softmax(attn, 1)) */
+#define L1ATTN_SV_SOFTMAX_PLUS_ONE 1 /* exp(x) / (1 + sum exp(x)): softmax with one more all-zero source row */
+#define L1ATTN_SV_EXP 2              /* exp(x), no normalisation */
+
 /* Library version (major*10000 + minor*100 + patch). */
 int l1attn_version(void);
 /* Static description of an L1ATTN_ERR_* code. */
@@ -85,6 +90,22 @@ int l1attn_dense_fwd(const void *q, const void *k, void *attn,
 size_t l1attn_dense_bwd_scratch_bytes(int bs, int n_tok, int n_heads, int width, int dtype);
 int l1attn_dense_bwd(const void *d_attn, const void *q, const void *k, void *d_q, void *d_k, void *scratch,
 		     int bs, int n_tok, int n_heads, int width, int dtype, void *stream);
+
+/*
+ * Dense scores, normalisation and value product in one pass, without the [bs, n_tok, n_tok, n_heads]
+ * score tensor:
+ *   x[b][s][t][h]  = (-1/sqrt(width)) * sum_w |q[b][t][h][w] - k[b][s][h][w]|
+ *   a              = softmax_s(x) | exp(x) / (1 + sum_s exp(x)) | exp(x)        (mode L1ATTN_SV_*)
+ *   vo[b][t][h][:] = sum_s a[b][s][t][h] * v[b][s][h][:]                         v, vo: [bs][n_tok][n_heads][v_width]
+ * The reference has no single function for this: it is the sequence every dense caller runs right
+ * after l1attn_cuda.L1Attn -- F.softmax(a, 1) and einsum('bsdh,bshw->bdhw') (README.md:64-66,
+ * testdense.py:14-16) -- and its README (README.md:21) names the fusion as the goal.  The "+1" and
+ * exp forms are the dense equivalents of the sparse operator's weights
+ * (python/l1attn_sparse.py:491-502).  Forward only; no scratch memory.
+ */
+int l1attn_dense_softmax_v_fwd(const void *q, const void *k, const void *v, void *vo,
+			       int bs, int n_tok, int n_heads, int width, int v_width,
+			       int mode, int dtype, void *stream);
 
 /* ------------------------------------------------------------------ sparse -------------- */
 
@@ -175,6 +196,8 @@ int l1attn_i64_minmax(const int64_t *x, long long n, int64_t *out, void *stream)
 /* Same operations with every tensor in HOST memory (pageable or pinned); synchronous. */
 int l1attn_dense_fwd_host(const void *q, const void *k, void *attn,
 			  int bs, int n_tok, int n_heads, int width, int dtype);
+int l1attn_dense_softmax_v_fwd_host(const void *q, const void *k, const void *v, void *vo,
+				    int bs, int n_tok, int n_heads, int width, int v_width, int mode, int dtype);
 int l1attn_dense_bwd_host(const void *d_attn, const void *q, const void *k, void *d_q, void *d_k,
 			  int bs, int n_tok, int n_heads, int width, int dtype);
 int l1attn_sparse_fwd_host(const void *v, const void *vb, const void *q, const void *k, const int32_t *coo,

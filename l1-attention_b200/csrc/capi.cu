@@ -116,6 +116,19 @@ extern "C" int l1attn_dense_fwd(const void *q, const void *k, void *attn, int bs
 	return dense_fwd_launch(q, k, attn, bs, n_tok, n_heads, width, dtype, static_cast<cudaStream_t>(stream));
 }
 
+extern "C" int l1attn_dense_softmax_v_fwd(const void *q, const void *k, const void *v, void *vo, int bs, int n_tok,
+					   int n_heads, int width, int v_width, int mode, int dtype, void *stream)
+{
+	const void *ptrs[] = {q, k, v, vo};
+	int rc = check_dense(ptrs, 4, bs, n_tok, n_heads, width, dtype);
+	if (rc)
+		return rc;
+	if (v_width < 1 || mode < L1ATTN_SV_SOFTMAX || mode > L1ATTN_SV_EXP)
+		return L1ATTN_ERR_ARG;
+	return dense_softmax_v_launch(q, k, v, vo, bs, n_tok, n_heads, width, v_width, mode, dtype,
+				      static_cast<cudaStream_t>(stream));
+}
+
 extern "C" size_t l1attn_dense_bwd_scratch_bytes(int bs, int n_tok, int n_heads, int width, int dtype)
 {
 	return dense_bwd_scratch_bytes(bs, n_tok, n_heads, width, dtype);
@@ -160,6 +173,36 @@ extern "C" int l1attn_dense_fwd_host(const void *q, const void *k, void *attn, i
 	if ((rc = dense_fwd_launch(dq, dk, da, bs, n_tok, n_heads, width, dtype, 0)))
 		return rc;
 	D2H(attn, da, na);
+	L1B_CUDA(cudaStreamSynchronize(0));
+	return L1ATTN_OK;
+}
+
+extern "C" int l1attn_dense_softmax_v_fwd_host(const void *q, const void *k, const void *v, void *vo, int bs, int n_tok,
+						int n_heads, int width, int v_width, int mode, int dtype)
+{
+	const void *ptrs[] = {q, k, v, vo};
+	int rc = check_dense(ptrs, 4, bs, n_tok, n_heads, width, dtype);
+	if (rc)
+		return rc;
+	if (v_width < 1 || mode < L1ATTN_SV_SOFTMAX || mode > L1ATTN_SV_EXP)
+		return L1ATTN_ERR_ARG;
+	const size_t es = dtype == L1ATTN_F64 ? 8 : 4;
+	const size_t nqk = size_t(bs) * n_tok * n_heads * width * es, nv = size_t(bs) * n_tok * n_heads * v_width * es;
+	if (nv == 0)
+		return L1ATTN_OK;
+	std::lock_guard<std::mutex> lock(g_mu);
+	Arena *ar = arena_for_current(&rc);
+	if (!ar)
+		return rc;
+	if ((rc = arena_reserve(ar, 2 * pad256(nqk) + 2 * pad256(nv))))
+		return rc;
+	void *dq = arena_take(ar, nqk), *dk = arena_take(ar, nqk), *dv = arena_take(ar, nv), *dvo = arena_take(ar, nv);
+	H2D(dq, q, nqk);
+	H2D(dk, k, nqk);
+	H2D(dv, v, nv);
+	if ((rc = dense_softmax_v_launch(dq, dk, dv, dvo, bs, n_tok, n_heads, width, v_width, mode, dtype, 0)))
+		return rc;
+	D2H(vo, dvo, nv);
 	L1B_CUDA(cudaStreamSynchronize(0));
 	return L1ATTN_OK;
 }

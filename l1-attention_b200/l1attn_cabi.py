@@ -26,6 +26,7 @@ SIGNATURES = {
     "l1attn_last_cuda_error": (_i, []),
     "l1attn_device_status": (_i, []),
     "l1attn_dense_fwd": (_i, [_vp] * 3 + [_i] * 5 + [_vp]),
+    "l1attn_dense_softmax_v_fwd": (_i, [_vp] * 4 + [_i] * 7 + [_vp]),
     "l1attn_dense_bwd_scratch_bytes": (_sz, [_i] * 5),
     "l1attn_dense_bwd": (_i, [_vp] * 6 + [_i] * 5 + [_vp]),
     "l1attn_sparse_index_bytes": (_sz, [_i] * 3),
@@ -39,6 +40,7 @@ SIGNATURES = {
     "l1attn_expand_coo": (_i, [_vp, _i, _vp, _vp, _ll, _ll, _vp, _vp]),
     "l1attn_i64_minmax": (_i, [_vp, _ll, _vp, _vp]),
     "l1attn_dense_fwd_host": (_i, [_vp] * 3 + [_i] * 5),
+    "l1attn_dense_softmax_v_fwd_host": (_i, [_vp] * 4 + [_i] * 7),
     "l1attn_dense_bwd_host": (_i, [_vp] * 5 + [_i] * 5),
     "l1attn_sparse_fwd_host": (_i, [_vp] * 7 + [_i] * 10),
     "l1attn_sparse_bwd_host": (_i, [_vp] * 11 + [_i] * 10),
@@ -100,6 +102,20 @@ def dense_fwd_host(q, k, out=None):
     attn = np.empty((bs, n, n, h), dtype=q.dtype) if out is None else out
     _check(lib().l1attn_dense_fwd_host(_ptr(q), _ptr(k), _ptr(attn), bs, n, h, w, _dt(q)), "l1attn_dense_fwd_host")
     return attn
+
+
+SV_MODES = {"softmax": 0, "softmax_plus_one": 1, "exp": 2}
+
+
+def dense_softmax_v_fwd_host(q, k, v, mode="softmax"):
+    """vo = sum_s a[b,s,t,h] v[b,s,h,:] with a = the chosen normalisation of the L1 scores (numpy in/out)."""
+    q = _np(q)
+    k, v = _np(k, q.dtype), _np(v, q.dtype)
+    bs, n, h, w = q.shape
+    vo = np.empty_like(v)
+    _check(lib().l1attn_dense_softmax_v_fwd_host(_ptr(q), _ptr(k), _ptr(v), _ptr(vo), bs, n, h, w, v.shape[3],
+                                                 SV_MODES[mode], _dt(q)), "l1attn_dense_softmax_v_fwd_host")
+    return vo
 
 
 def dense_bwd_host(d_attn, q, k, out=None):
@@ -183,6 +199,18 @@ def dense_fwd(q, k, out=None):
     attn = torch.empty((bs, n, n, h), dtype=q.dtype, device=q.device) if out is None else out
     _check(lib().l1attn_dense_fwd(_dp(q), _dp(k), _dp(attn), bs, n, h, w, _tdt(q), _stream()), "l1attn_dense_fwd")
     return attn
+
+
+def dense_softmax_v_fwd(q, k, v, mode="softmax", out=None):
+    """q, k: [bs, n, h, w], v: [bs, n, h, wv], contiguous CUDA tensors.  Enqueues on the current stream."""
+    import torch
+    assert q.is_cuda and q.is_contiguous() and k.is_contiguous() and v.is_contiguous()
+    assert k.shape == q.shape and v.shape[:3] == q.shape[:3] and k.dtype == q.dtype and v.dtype == q.dtype
+    bs, n, h, w = q.shape
+    vo = torch.empty_like(v) if out is None else out
+    _check(lib().l1attn_dense_softmax_v_fwd(_dp(q), _dp(k), _dp(v), _dp(vo), bs, n, h, w, v.shape[3], SV_MODES[mode],
+                                            _tdt(q), _stream()), "l1attn_dense_softmax_v_fwd")
+    return vo
 
 
 def dense_bwd(d_attn, q, k, out=None, scratch="auto"):

@@ -69,6 +69,53 @@ void FN(oracle_dense_bwd)(const REAL *d_attn, const REAL *q, const REAL *k, REAL
 				}
 }
 
+
+/*
+ * The dense consumer that follows l1attn_forward in every dense caller of the reference
+ * (README.md:64-66, testdense.py:14-16): a = F.softmax(attn, 1); vo = einsum('bsdh,bshw->bdhw', a, v).
+ * mode 0: softmax over s (max subtracted first, as torch does);
+ * mode 1: softmax with one more all-zero source row, the row then dropped
+ *         (python/l1attn_sparse.py:491-502: zero-padded `ap`, softmax, strip) = exp(x) / (1 + sum exp(x)),
+ *         the maximum being the 0 of the extra row;
+ * mode 2: exp(x) (same lines, use_softmax False).
+ * `attn` is scratch of n_ctx REALs.
+ */
+void FN(oracle_dense_softmax_v)(const REAL *q, const REAL *k, const REAL *v, REAL *vo, REAL *attn, int bs, int n_ctx,
+				int n_heads, int width, int v_width, int mode)
+{
+	const double scale = -1.0 / sqrt((double)width);
+	for (int b = 0; b < bs; b++)
+		for (int t = 0; t < n_ctx; t++)
+			for (int h = 0; h < n_heads; h++) {
+				const REAL *qr = q + (((size_t)b * n_ctx + t) * n_heads + h) * width;
+				REAL mx = 0; /* modes 1, 2: the extra row's 0 / no shift */
+				for (int s = 0; s < n_ctx; s++) {
+					const REAL *kr = k + (((size_t)b * n_ctx + s) * n_heads + h) * width;
+					REAL f = 0;
+					for (int w = 0; w < width; w++)
+						f += ABS(qr[w] - kr[w]);
+					f *= scale;
+					attn[s] = f;
+					if (mode == 0 && (s == 0 || f > mx))
+						mx = f;
+				}
+				REAL den = mode == 1 ? (REAL)1 : (REAL)0;
+				for (int s = 0; s < n_ctx; s++) {
+					attn[s] = EXP(attn[s] - mx);
+					den += attn[s];
+				}
+				if (mode == 2)
+					den = 1;
+				REAL *o = vo + (((size_t)b * n_ctx + t) * n_heads + h) * v_width;
+				for (int c = 0; c < v_width; c++) {
+					REAL acc = 0;
+					for (int s = 0; s < n_ctx; s++)
+						acc += attn[s] * v[(((size_t)b * n_ctx + s) * n_heads + h) * v_width + c];
+					o[c] = acc / den;
+				}
+			}
+}
+
 /*
  * Sparse forward, one-directional (bidi == 0; cpp/l1attn_sparse_drv.cpp:13-96) or bidirectional
  * (bidi == 1; cpp/l1attn_sparse_bidi_drv.cpp:15-101).  `v` is V (vf for bidi); `vb` is read only

@@ -69,6 +69,20 @@ def dense_bwd(d_attn, q, k):
     return dq, dk
 
 
+SV_MODES = {"softmax": 0, "softmax_plus_one": 1, "exp": 2}
+
+
+def dense_softmax_v(q, k, v, mode="softmax"):
+    """vo[b,t,h,:] = sum_s a[b,s,t,h] v[b,s,h,:], a = softmax / "+1" softmax / exp of the dense L1 scores."""
+    q = _c(q)
+    k, v = _c(k, q.dtype), _c(v, q.dtype)
+    bs, n, h, w = q.shape
+    vo, scratch = np.empty_like(v), np.empty(max(n, 1), dtype=q.dtype)
+    getattr(lib(), "oracle_dense_softmax_v_" + _sfx(q))(_p(q), _p(k), _p(v), _p(vo), _p(scratch), bs, n, h, w,
+                                                        v.shape[3], SV_MODES[mode])
+    return vo
+
+
 def _coo(coo):
     coo = _c(coo, np.int32)
     assert coo.ndim == 2 and coo.shape[1] == 4, "coo must be [cl,4] (output of expandCoo)"

@@ -44,4 +44,4 @@ def assert_close(x, ref, tol, what=""):
 @pytest.fixture(scope="session")
 def golden():
     d = os.path.join(ROOT, "tests", "golden")
-    return {n: np.load(os.path.join(d, n + ".npz")) for n in ("kat", "dense", "sparse", "expandcoo")}
+    return {n: np.load(os.path.join(d, n + ".npz")) for n in ("kat", "dense", "sparse", "expandcoo", "fused")}

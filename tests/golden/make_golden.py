@@ -16,6 +16,7 @@ Files written:
   dense.npz    seeded dense cases (incl. ties and zero-padded tokens), fwd + grads
   sparse.npz   seeded sparse / bidi cases (cartesian, permuted, rows dropped, ragged), fwd + grads
   expandcoo.npz  expandCoo inputs and outputs
+  fused.npz    dense consumer chain (scores -> softmax / "+1" softmax / exp -> value product)
 """
 import argparse
 import os
@@ -204,6 +205,33 @@ def sparse_cases(ref_sparse, cpp):
     return out
 
 
+def fused_cases(ref_dense_naive):
+    """Dense consumer chain run with the reference's own L1Attn module (python/l1attn.py):
+    README.md:64-66 (softmax over dim 1, then einsum) and the zero-padded "+1" variant of
+    python/l1attn_sparse.py:491-502 (with and without softmax)."""
+    import torch.nn.functional as F
+    out, names = {}, []
+    g = torch.Generator().manual_seed(20243)
+    for name, shape, wv in [("readme", (2, 3, 4, 8), 8), ("w32", (1, 70, 2, 32), 32), ("odd", (1, 9, 2, 7), 5),
+                            ("far", (1, 20, 2, 64), 64)]:
+        bs, n, h, w = shape
+        q = torch.randn(shape, generator=g, dtype=torch.float64)
+        k = torch.randn(shape, generator=g, dtype=torch.float64)
+        if name == "far":  # every score far below zero: the plain softmax must shift by the maximum
+            k = k + 40.0
+        v = torch.randn((bs, n, h, wv), generator=g, dtype=torch.float64)
+        a = ref_dense_naive.L1Attn()(q, k)
+        out[name + "_q"], out[name + "_k"], out[name + "_v"] = np_(q), np_(k), np_(v)
+        out[name + "_softmax"] = np_(torch.einsum("bsdh, bshw -> bdhw", F.softmax(a, 1), v))
+        ap = torch.zeros(bs, n + 1, n + 1, h, dtype=torch.float64)
+        ap[:, :-1, :-1, :] = a
+        out[name + "_softmax_plus_one"] = np_(torch.einsum("bsdh, bshw -> bdhw", F.softmax(ap, 1)[:, :-1, :-1, :], v))
+        out[name + "_exp"] = np_(torch.einsum("bsdh, bshw -> bdhw", torch.exp(ap)[:, :-1, :-1, :], v))
+        names.append(name)
+    out["names"] = np.array(names)
+    return out
+
+
 def expandcoo_cases(ref_sparse):
     out = {}
     g = torch.Generator().manual_seed(20243)
@@ -232,16 +260,21 @@ def expandcoo_cases(ref_sparse):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--ref", required=True)
+    ap.add_argument("--only", default="", help="comma-separated fixture names (default: all)")
     a = ap.parse_args()
     ref_dense_naive, ref_dense_fn, ref_sparse, cpp = load_reference(a.ref)
     if not cpp:
         print("note: oracle/_ref not built -- *_cpp arrays are omitted (tests then skip the bit-exact checks)")
     torch.manual_seed(0)
-    np.savez_compressed(os.path.join(HERE, "kat.npz"), **kat(ref_dense_naive, ref_sparse))
-    np.savez_compressed(os.path.join(HERE, "dense.npz"), **dense_cases(ref_dense_naive, ref_dense_fn, cpp))
-    np.savez_compressed(os.path.join(HERE, "sparse.npz"), **sparse_cases(ref_sparse, cpp))
-    np.savez_compressed(os.path.join(HERE, "expandcoo.npz"), **expandcoo_cases(ref_sparse))
-    for f in ("kat", "dense", "sparse", "expandcoo"):
+    makers = {
+        "kat": lambda: kat(ref_dense_naive, ref_sparse),
+        "dense": lambda: dense_cases(ref_dense_naive, ref_dense_fn, cpp),
+        "sparse": lambda: sparse_cases(ref_sparse, cpp),
+        "expandcoo": lambda: expandcoo_cases(ref_sparse),
+        "fused": lambda: fused_cases(ref_dense_naive),
+    }
+    for f in (a.only.split(",") if a.only else makers):
+        np.savez_compressed(os.path.join(HERE, f + ".npz"), **makers[f]())
         print(f, os.path.getsize(os.path.join(HERE, f + ".npz")), "bytes")
 
 

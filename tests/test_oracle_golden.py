@@ -135,3 +135,19 @@ def test_expandcoo_golden(golden):
 def test_expandcoo_empty():
     coo, dm, sm = oracle.expand_coo(np.zeros((0, 2), dtype=np.int64))
     assert coo.shape == (0, 4) and (dm, sm) == (1, 1)
+
+
+@pytest.mark.parametrize("mode", ["softmax", "softmax_plus_one", "exp"])
+def test_dense_softmax_v_golden(golden, mode):
+    """Scores -> normalisation -> value product as the reference's own modules compute it
+    (README.md:64-66 and the zero-padded "+1" forms of python/l1attn_sparse.py:491-502)."""
+    g = golden["fused"]
+    for name in g["names"]:
+        q, k, v = g[name + "_q"], g[name + "_k"], g[name + "_v"]
+        # 'far' holds scores near -320: exp() there amplifies the last-bit differences of the scores
+        assert_close(oracle.dense_softmax_v(q, k, v, mode), g["%s_%s" % (name, mode)],
+                     1e-11 if name == "far" else TOL64, "%s %s" % (name, mode))
+    # testdense.py:20-39 one-hot fixture, softmax form
+    k3 = golden["kat"]
+    if mode == "softmax":
+        assert_close(oracle.dense_softmax_v(k3["f3_q"], k3["f3_k"], k3["f3_v"], mode), k3["f3_vo"], 1e-6, "testdense fixture")
