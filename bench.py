@@ -44,6 +44,10 @@ WORKLOADS = {
     "sparse_cfg4": dict(kind="sparse", shape=(8, 4096, 8, 64), fan=31),
     # BASELINE config 5: training step of a 4-layer pre-LN transformer on L1AttnSparseBidi; not a model of
     # the reference (it ships none for the sparse operator), written here from the config's description
+    # the dense scores fused with softmax and the value product (no [B,T,T,H] tensor): benchmark and long-context shapes
+    "fused_cfg2": dict(kind="fused", shape=(16, 1024, 16, 64)),
+    "fused_cfg3": dict(kind="fused", shape=(2, 4096, 8, 128)),
+    "fused_small": dict(kind="fused", shape=(2, 1024, 16, 64)),
     "train_cfg5": dict(kind="train", batch=64, seq=256, d_model=256, heads=8, layers=4, vocab=64, fan=16),
 }
 SM_COUNT, FP32_LANES = 148, 128
@@ -363,6 +367,80 @@ def run_train(args, wl):
     print(json.dumps(line), flush=True)
 
 
+def run_fused(args, wl):
+    """Forward and forward+backward of l1attn_fused_cuda.L1AttnSoftmaxV beside the unfused chain the
+    reference's callers write (library scores -> torch softmax -> torch einsum), with peak memory."""
+    import torch
+    import l1attn_cabi
+    import l1attn_cuda
+    import l1attn_fused_cuda
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device -- this library has no CPU path")
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    bs, n, h, w = wl["shape"]
+    gen = torch.Generator(device=dev).manual_seed(6001)
+    q, k = (0.3 * torch.randn(bs, n, h, w, device=dev, generator=gen) for _ in range(2))
+    v, g = (torch.randn(bs, n, h, w, device=dev, generator=gen) for _ in range(2))
+    warm = max(args.warmup, 3)
+
+    def timed(fn):
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize()
+        torch.cuda.reset_peak_memory_stats(dev)
+        base = torch.cuda.memory_allocated(dev)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / args.steps, (torch.cuda.max_memory_allocated(dev) - base) / 2 ** 20
+
+    out = torch.empty_like(v)
+    fwd_ms, _ = timed(lambda: l1attn_cabi.dense_softmax_v_fwd(q, k, v, "softmax", out=out))
+    qr, kr, vr = (t.clone().requires_grad_(True) for t in (q, k, v))
+    fused_mod = l1attn_fused_cuda.L1AttnSoftmaxV("softmax")
+    dense_mod = l1attn_cuda.L1Attn()
+
+    def fused_step():
+        for t in (qr, kr, vr):
+            t.grad = None
+        fused_mod(qr, kr, vr).backward(g)
+
+    def unfused_step():
+        for t in (qr, kr, vr):
+            t.grad = None
+        torch.einsum("bsdh,bshw->bdhw", torch.softmax(dense_mod(qr, kr), 1), vr).backward(g)
+
+    def unfused_fwd():
+        with torch.no_grad():
+            torch.einsum("bsdh,bshw->bdhw", torch.softmax(dense_mod(q, k), 1), v)
+
+    step_ms, step_mib = timed(fused_step)
+    ufwd_ms, ufwd_mib = timed(unfused_fwd)
+    ustep_ms, ustep_mib = timed(unfused_step)
+    ops = bs * h * n * n * w
+    # forward instruction floor per (t, s, w) term: 1.5 issue slots for the score + 1 FMA of the value
+    # product (v_width = width) against 4 issue slots per clock per SM
+    sm_mhz, sms = 1965.0, 148
+    floor_ms = ops * 2.5 / 32 / (4 * sms * sm_mhz * 1e6) * 1e3
+    line = {"metric": "fused dense L1 attention (scores+softmax+V) forward Gop/s (B*H*T^2*W)", "value": ops / (fwd_ms * 1e-3) / 1e9,
+            "unit": "Gop/s", "n_gpus": 1, "steps": args.steps, "warmup": warm, "ms_per_step": fwd_ms,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "%s: %dx%dx%dx%d, v_width %d" % (args.workload, bs, n, h, w, w)},
+            "fwd_ms": fwd_ms, "fwd_bwd_ms": step_ms, "fwd_bwd_peak_extra_mib": step_mib,
+            "issue_floor": {"ms": floor_ms, "frac": floor_ms / fwd_ms,
+                            "model": "2.5 warp instructions per 32 terms, 4 issue slots/clk/SM, 148 SMs, 1965 MHz"},
+            "unfused": {"fwd_ms": ufwd_ms, "fwd_peak_extra_mib": ufwd_mib, "fwd_bwd_ms": ustep_ms,
+                        "fwd_bwd_peak_extra_mib": ustep_mib,
+                        "chain": "l1attn_cuda.L1Attn -> torch.softmax(dim=1) -> torch.einsum('bsdh,bshw->bdhw')"},
+            "gpu_launches": args.steps}
+    print(json.dumps(line), flush=True)
+
+
 # ----------------------------------------------------------------------------- our arm
 
 def run_ours(args, wl):
@@ -580,6 +658,12 @@ def main():
                               "extension has no training loop; use --compare-reference-cuda on the default arm"}))
         else:
             run_train(args, wl)
+    elif wl["kind"] == "fused":
+        if args.impl == "reference":
+            print(json.dumps({"impl": "reference", "unavailable": "the reference has no fused operator; its CPU "
+                              "arm is measured on the dense workloads"}))
+        else:
+            run_fused(args, wl)
     elif args.impl == "reference":
         run_reference_arm(args, wl)
     else:

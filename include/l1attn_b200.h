@@ -101,11 +101,29 @@ int l1attn_dense_bwd(const void *d_attn, const void *q, const void *k, void *d_q
  * after l1attn_cuda.L1Attn -- F.softmax(a, 1) and einsum('bsdh,bshw->bdhw') (README.md:64-66,
  * testdense.py:14-16) -- and its README (README.md:21) names the fusion as the goal.  The "+1" and
  * exp forms are the dense equivalents of the sparse operator's weights
- * (python/l1attn_sparse.py:491-502).  Forward only; no scratch memory.
+ * (python/l1attn_sparse.py:491-502).  No scratch memory.
+ * lse: NULL, or [bs][n_tok][n_heads] receiving the log of each query row's normaliser (weight of
+ * (s, t) = exp(x - lse); zeros for L1ATTN_SV_EXP) -- what l1attn_dense_softmax_v_bwd_dx needs.
  */
-int l1attn_dense_softmax_v_fwd(const void *q, const void *k, const void *v, void *vo,
+int l1attn_dense_softmax_v_fwd(const void *q, const void *k, const void *v, void *vo, void *lse,
 			       int bs, int n_tok, int n_heads, int width, int v_width,
 			       int mode, int dtype, void *stream);
+
+/*
+ * First half of the backward of l1attn_dense_softmax_v_fwd (no counterpart in the reference either):
+ *   p              = exp(x[b][s][t][h] - lse[b][t][h])
+ *   dx[b][s][t][h] = p * (<v[b][s][h][:], dvo[b][t][h][:]> - delta[b][t][h])
+ *   dv[b][s][h][:] = sum_t p * dvo[b][t][h][:]
+ * with delta[b][t][h] = <dvo[b][t][h][:], vo[b][t][h][:]> for the two softmax forms and zeros for
+ * L1ATTN_SV_EXP (the caller computes it: one elementwise product and a row sum).  dx has the layout
+ * of d_attn, so l1attn_dense_bwd(dx, q, k, d_q, d_k, ...) is the second half.  Only dx is of size
+ * n_tok x n_tok; callers bound it by passing a few batch items per call (every pointer advanced to
+ * the first item of the chunk, bs = items in the chunk).
+ */
+int l1attn_dense_softmax_v_bwd_dx(const void *q, const void *k, const void *v, const void *dvo,
+				  const void *lse, const void *delta, void *dx, void *dv,
+				  int bs, int n_tok, int n_heads, int width, int v_width,
+				  int dtype, void *stream);
 
 /* ------------------------------------------------------------------ sparse -------------- */
 

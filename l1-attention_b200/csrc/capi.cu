@@ -116,7 +116,7 @@ extern "C" int l1attn_dense_fwd(const void *q, const void *k, void *attn, int bs
 	return dense_fwd_launch(q, k, attn, bs, n_tok, n_heads, width, dtype, static_cast<cudaStream_t>(stream));
 }
 
-extern "C" int l1attn_dense_softmax_v_fwd(const void *q, const void *k, const void *v, void *vo, int bs, int n_tok,
+extern "C" int l1attn_dense_softmax_v_fwd(const void *q, const void *k, const void *v, void *vo, void *lse, int bs, int n_tok,
 					   int n_heads, int width, int v_width, int mode, int dtype, void *stream)
 {
 	const void *ptrs[] = {q, k, v, vo};
@@ -125,8 +125,24 @@ extern "C" int l1attn_dense_softmax_v_fwd(const void *q, const void *k, const vo
 		return rc;
 	if (v_width < 1 || mode < L1ATTN_SV_SOFTMAX || mode > L1ATTN_SV_EXP)
 		return L1ATTN_ERR_ARG;
-	return dense_softmax_v_launch(q, k, v, vo, bs, n_tok, n_heads, width, v_width, mode, dtype,
+	if (lse && !aligned(lse, dtype == L1ATTN_F64 ? 8 : 4))
+		return L1ATTN_ERR_ALIGN;
+	return dense_softmax_v_launch(q, k, v, vo, lse, bs, n_tok, n_heads, width, v_width, mode, dtype,
 				      static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int l1attn_dense_softmax_v_bwd_dx(const void *q, const void *k, const void *v, const void *dvo, const void *lse,
+					      const void *delta, void *dx, void *dv, int bs, int n_tok, int n_heads, int width,
+					      int v_width, int dtype, void *stream)
+{
+	const void *ptrs[] = {q, k, v, dvo, lse, delta, dx, dv};
+	int rc = check_dense(ptrs, 8, bs, n_tok, n_heads, width, dtype);
+	if (rc)
+		return rc;
+	if (v_width < 1)
+		return L1ATTN_ERR_ARG;
+	return dense_softmax_v_bwd_dx_launch(q, k, v, dvo, lse, delta, dx, dv, bs, n_tok, n_heads, width, v_width, dtype,
+					     static_cast<cudaStream_t>(stream));
 }
 
 extern "C" size_t l1attn_dense_bwd_scratch_bytes(int bs, int n_tok, int n_heads, int width, int dtype)
@@ -200,7 +216,7 @@ extern "C" int l1attn_dense_softmax_v_fwd_host(const void *q, const void *k, con
 	H2D(dq, q, nqk);
 	H2D(dk, k, nqk);
 	H2D(dv, v, nv);
-	if ((rc = dense_softmax_v_launch(dq, dk, dv, dvo, bs, n_tok, n_heads, width, v_width, mode, dtype, 0)))
+	if ((rc = dense_softmax_v_launch(dq, dk, dv, dvo, nullptr, bs, n_tok, n_heads, width, v_width, mode, dtype, 0)))
 		return rc;
 	D2H(vo, dvo, nv);
 	L1B_CUDA(cudaStreamSynchronize(0));

@@ -78,8 +78,11 @@ int dense_ties_launch(const float *q, const float *k, unsigned char *flags, int 
 int dense_bwd_launch(const void *d_attn, const void *q, const void *k, void *d_q, void *d_k, void *scratch, int bs,
 		     int n_tok, int n_heads, int width, int dtype, cudaStream_t st);
 size_t dense_bwd_scratch_bytes(int bs, int n_tok, int n_heads, int width, int dtype);
-int dense_softmax_v_launch(const void *q, const void *k, const void *v, void *vo, int bs, int n_tok, int n_heads, int width,
-			   int v_width, int mode, int dtype, cudaStream_t st);
+int dense_softmax_v_launch(const void *q, const void *k, const void *v, void *vo, void *lse, int bs, int n_tok, int n_heads,
+			   int width, int v_width, int mode, int dtype, cudaStream_t st);
+int dense_softmax_v_bwd_dx_launch(const void *q, const void *k, const void *v, const void *dvo, const void *lse,
+				  const void *delta, void *dx, void *dv, int bs, int n_tok, int n_heads, int width, int v_width,
+				  int dtype, cudaStream_t st);
 
 // Layout of the sparse edge index (all int32, each array padded to 16 bytes):
 //   slot_src [n_tok*dst_mxlen]  src token of slot (dst, r), or -1

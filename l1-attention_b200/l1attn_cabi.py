@@ -26,7 +26,8 @@ SIGNATURES = {
     "l1attn_last_cuda_error": (_i, []),
     "l1attn_device_status": (_i, []),
     "l1attn_dense_fwd": (_i, [_vp] * 3 + [_i] * 5 + [_vp]),
-    "l1attn_dense_softmax_v_fwd": (_i, [_vp] * 4 + [_i] * 7 + [_vp]),
+    "l1attn_dense_softmax_v_fwd": (_i, [_vp] * 5 + [_i] * 7 + [_vp]),
+    "l1attn_dense_softmax_v_bwd_dx": (_i, [_vp] * 8 + [_i] * 6 + [_vp]),
     "l1attn_dense_bwd_scratch_bytes": (_sz, [_i] * 5),
     "l1attn_dense_bwd": (_i, [_vp] * 6 + [_i] * 5 + [_vp]),
     "l1attn_sparse_index_bytes": (_sz, [_i] * 3),
@@ -201,16 +202,28 @@ def dense_fwd(q, k, out=None):
     return attn
 
 
-def dense_softmax_v_fwd(q, k, v, mode="softmax", out=None):
-    """q, k: [bs, n, h, w], v: [bs, n, h, wv], contiguous CUDA tensors.  Enqueues on the current stream."""
+def dense_softmax_v_fwd(q, k, v, mode="softmax", out=None, lse=None):
+    """q, k: [bs, n, h, w], v: [bs, n, h, wv], contiguous CUDA tensors.  Enqueues on the current stream.
+    lse: optional [bs, n, h] tensor receiving the log-normalisers (needed by dense_softmax_v_bwd_dx)."""
     import torch
     assert q.is_cuda and q.is_contiguous() and k.is_contiguous() and v.is_contiguous()
     assert k.shape == q.shape and v.shape[:3] == q.shape[:3] and k.dtype == q.dtype and v.dtype == q.dtype
     bs, n, h, w = q.shape
     vo = torch.empty_like(v) if out is None else out
-    _check(lib().l1attn_dense_softmax_v_fwd(_dp(q), _dp(k), _dp(v), _dp(vo), bs, n, h, w, v.shape[3], SV_MODES[mode],
-                                            _tdt(q), _stream()), "l1attn_dense_softmax_v_fwd")
+    assert lse is None or (lse.is_contiguous() and lse.shape == q.shape[:3] and lse.dtype == q.dtype)
+    _check(lib().l1attn_dense_softmax_v_fwd(_dp(q), _dp(k), _dp(v), _dp(vo), _dp(lse), bs, n, h, w, v.shape[3],
+                                            SV_MODES[mode], _tdt(q), _stream()), "l1attn_dense_softmax_v_fwd")
     return vo
+
+
+def dense_softmax_v_bwd_dx(q, k, v, dvo, lse, delta, dx, dv):
+    """Fills dx [bs, n, n, h] (layout of d_attn) and dv [bs, n, h, wv]; all tensors contiguous, same dtype."""
+    for t in (q, k, v, dvo, lse, delta, dx, dv):
+        assert t.is_cuda and t.is_contiguous() and t.dtype == q.dtype
+    bs, n, h, w = q.shape
+    assert dx.shape == (bs, n, n, h) and dv.shape == v.shape and lse.shape == (bs, n, h) and delta.shape == (bs, n, h)
+    _check(lib().l1attn_dense_softmax_v_bwd_dx(_dp(q), _dp(k), _dp(v), _dp(dvo), _dp(lse), _dp(delta), _dp(dx), _dp(dv),
+                                               bs, n, h, w, v.shape[3], _tdt(q), _stream()), "l1attn_dense_softmax_v_bwd_dx")
 
 
 def dense_bwd(d_attn, q, k, out=None, scratch="auto"):

@@ -11,11 +11,11 @@ and its README (README.md:21) names doing this without the [bs, n, n, h] tensor 
 equivalents of the sparse operator's weights (python/l1attn_sparse.py:491-502: softmax with one more
 all-zero source row, or plain exp).  `l1attn_cuda.L1Attn` itself is unchanged.
 
-Forward: one kernel (`l1attn_dense_softmax_v_fwd`), nothing of size n x n is stored.
-Backward: recomputes the scores a few batch items at a time with the library's dense forward,
-applies the softmax/value-product derivatives with torch ops on that chunk and feeds the result to
-the library's dense backward, so the peak extra memory is a few chunk-sized [c, n, n, h] tensors
-instead of four full ones.
+Forward: one kernel (`l1attn_dense_softmax_v_fwd`), nothing of size n x n is stored; it keeps the log
+of every query row's normaliser ([bs, n, h]) for the backward.
+Backward, a few batch items at a time: `l1attn_dense_softmax_v_bwd_dx` recomputes the weights and
+writes the score gradients dx [c, n, n, h] and dv; the library's dense backward turns dx into dq, dk.
+The only n x n tensor alive is that one chunk of dx (256 MB by default).
 """
 import torch
 
@@ -38,40 +38,29 @@ class L1AttnSoftmaxVFn(torch.autograd.Function):
         if q.dtype not in (torch.float32, torch.float64) or k.dtype != q.dtype or v.dtype != q.dtype:
             raise RuntimeError("q, k, v must share dtype float32 or float64")
         q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        lse = torch.empty(q.shape[:3], dtype=q.dtype, device=q.device)
         with torch.cuda.device(q.device):
-            vo = _c.dense_softmax_v_fwd(q, k, v, mode)
-        ctx.save_for_backward(q, k, v)
+            vo = _c.dense_softmax_v_fwd(q, k, v, mode, lse=lse)
+        ctx.save_for_backward(q, k, v, vo, lse)
         ctx.mode = mode
         return vo
 
     @staticmethod
     def backward(ctx, dvo):
-        q, k, v = ctx.saved_tensors
-        mode = ctx.mode
+        q, k, v, vo, lse = ctx.saved_tensors
         dvo = dvo.contiguous()
         bs, n, h, _ = q.shape
         dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
-        step = max(1, _CHUNK_BYTES // max(1, n * n * h * q.element_size()))
+        # delta[b,t,h] = sum_s weight * <v_s, dvo_t> = <vo_t, dvo_t>; the exp form has no normaliser to differentiate
+        delta = torch.zeros_like(lse) if ctx.mode == "exp" else (dvo * vo).sum(-1)
+        step = max(1, min(bs, _CHUNK_BYTES // max(1, n * n * h * q.element_size())))
         with torch.cuda.device(q.device):
+            dx = torch.empty((step, n, n, h), dtype=q.dtype, device=q.device)
             for b0 in range(0, bs, step):
-                sl = slice(b0, min(bs, b0 + step))
-                qb, kb = q[sl], k[sl]  # leading-dimension slices of contiguous tensors stay contiguous
-                x = _c.dense_fwd(qb, kb)  # [c, s, t, h]
-                if mode == "softmax":
-                    a = torch.softmax(x, 1)
-                else:
-                    a = torch.exp(x)
-                    if mode == "softmax_plus_one":
-                        a = a / (1 + a.sum(1, keepdim=True))
-                del x
-                dv[sl] = torch.einsum("bsdh,bdhw->bshw", a, dvo[sl])
-                da = torch.einsum("bdhw,bshw->bsdh", dvo[sl], v[sl])
-                if mode == "exp":
-                    dx = a * da
-                else:  # the extra row of "+1" has a zero value vector, so the same Jacobian applies
-                    dx = a * (da - (a * da).sum(1, keepdim=True))
-                del a, da
-                _c.dense_bwd(dx.contiguous(), qb, kb, out=(dq[sl], dk[sl]))
+                sl = slice(b0, min(bs, b0 + step))  # leading-dimension slices of contiguous tensors stay contiguous
+                c = sl.stop - sl.start
+                _c.dense_softmax_v_bwd_dx(q[sl], k[sl], v[sl], dvo[sl], lse[sl], delta[sl], dx[:c], dv[sl])
+                _c.dense_bwd(dx[:c], q[sl], k[sl], out=(dq[sl], dk[sl]))
         return dq, dk, dv, None
 
 

@@ -91,12 +91,14 @@ def test_host_entry_point():
 
 @pytest.mark.parametrize("mode", MODES)
 @pytest.mark.parametrize("dtype", [torch.float64, torch.float32])
-def test_autograd_matches_the_unfused_chain(mode, dtype):
+@pytest.mark.parametrize("dims", [(2, 37, 3, 32, 32), (1, 150, 2, 64, 64), (1, 70, 2, 128, 128), (2, 66, 1, 64, 128),
+                                  (1, 20, 2, 7, 5)])
+def test_autograd_matches_the_unfused_chain(mode, dtype, dims):
     """Gradients of the fused module against torch autograd through the chain the reference's callers
     write (README.md:64-66), built here on pure-PyTorch scores."""
     import l1attn_fused_cuda
     torch.manual_seed(1)
-    bs, n, h, w, wv = 2, 37, 3, 32, 32
+    bs, n, h, w, wv = dims
     q = (0.3 * torch.randn(bs, n, h, w, dtype=dtype, device="cuda")).requires_grad_(True)
     k = (0.3 * torch.randn(bs, n, h, w, dtype=dtype, device="cuda")).requires_grad_(True)
     v = torch.randn(bs, n, h, wv, dtype=dtype, device="cuda", requires_grad=True)
