@@ -597,7 +597,7 @@ def run_ours(args, wl):
                     "achieved": alg_bytes / (bwd_ms * 1e-3) / 1e9,
                     "peak": pk["hbm_gbs"], "unit": "GB/s", "peak_source": pk["source"],
                     # ncu dram__bytes_read+write of this kernel at B=2,T=1024,H=16,W=64 (profiles/), scaled by batch
-                    "traffic": (311.8e6 * bs / 2.0) if (n, h, w) == (1024, 16, 64) else None,
+                    "traffic": (314.9e6 * bs / 2.0) if (n, h, w) == (1024, 16, 64) else None,
                     "note": "the kernel is FP32/ALU-pipe bound, not HBM bound: see alu_roofline"}
             roof["frac"] = roof["achieved"] / roof["peak"]
             mhz = (clocks or {}).get("sm_max_mhz") or pk["sm_max_mhz"]
