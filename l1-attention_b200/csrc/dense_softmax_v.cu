@@ -123,7 +123,7 @@ int launch_generic(const T *q, const T *k, const T *v, T *vo, T *lse, int bs, in
 // ------------------------------------------------------------------------------------------------
 // TMA kernel (fp32)
 // ------------------------------------------------------------------------------------------------
-// CTA = 8 warps = 16 half-warps.  Half-warp `tg` owns TI query rows (t = i*16 + tg) and is
+// CTA = NW warps = 2 NW half-warps.  Half-warp `tg` owns TI query rows (t = i*2*NW + tg) and is
 // self-contained: for every key tile its 16 lanes first each compute TI x 4 scores (keys
 // s = j*16 + lane), reduce the row maxima and sums by shuffles, park the weights in a private slice
 // of shared memory, and then each accumulate TI x NV output values (lane = value columns
@@ -131,7 +131,6 @@ int launch_generic(const T *q, const T *k, const T *v, T *vo, T *lse, int bs, in
 // Shared operand rows are 128 bytes (one 32-float slice of the width per TMA box, 128-byte swizzle),
 // so the 16 lanes of a half-warp read 16 different key rows without bank conflicts.
 constexpr int TS = 64;     // keys per ring stage
-constexpr int NTH = 256;
 constexpr int PP = TS + 4; // row pitch (floats) of the weight tile: the two half-warps of a warp land on different banks
 constexpr int MAX_STAGE = 3;
 
@@ -140,13 +139,14 @@ struct SvShape {
 	float scale;
 };
 
-template <int NV, int TI>
-__global__ void __launch_bounds__(NTH, 1)
+template <int NV, int TI, int NW>
+__global__ void __launch_bounds__(NW * 32, 1)
 softmax_v_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kmap,
 		     const __grid_constant__ CUtensorMap vmap, float *__restrict__ vo, float *__restrict__ lse, SvShape sh,
 		     int *err)
 {
-	constexpr int TT = 16 * TI;
+	constexpr int TT = 2 * NW * TI; // query rows of the CTA: a half-warp owns TI of them (t = i*2*NW + tg)
+	constexpr int NTH = NW * 32;
 	constexpr int VW = 16 * NV; // v_width
 	constexpr int V_BYTES = TS * VW * 4;
 	extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -211,7 +211,7 @@ softmax_v_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_cons
 	for (int m = 0; m < ns; m++) {
 		// one lane asks for the tile that will be needed nstage-1 tiles from now; its stage held tile
 		// m-1, which every warp must have released (the duty rotates so that no warp is always late)
-		if (warp == (m & 7) && lane == 0 && m + sh.nstage - 1 < ns && !dead) {
+		if (warp == m % NW && lane == 0 && m + sh.nstage - 1 < ns && !dead) {
 			const int mm = m + sh.nstage - 1;
 			if (mbar_wait(&empty_bar[mm % sh.nstage], ((unsigned(mm) / unsigned(sh.nstage)) & 1u) ^ 1u, err))
 				load_tile(mm);
@@ -243,7 +243,7 @@ softmax_v_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_cons
 					kv[j] = Kb[(j * 16 + sg) * 8 + (c ^ (sg & 7))];
 #pragma unroll
 				for (int i = 0; i < TI; i++) {
-					const ulonglong2 qv = Qb[(i * 16 + tg) * 8 + (c ^ (tg & 7))];
+					const ulonglong2 qv = Qb[(i * (2 * NW) + tg) * 8 + (c ^ (tg & 7))];
 #pragma unroll
 					for (int j = 0; j < 4; j++) {
 						unsigned long long d0, d1;
@@ -281,7 +281,7 @@ softmax_v_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_cons
 #pragma unroll
 			for (int j = 0; j < 4; j++) {
 				const float p = expf(x[j] - mnew);
-				Pw[i * 16 * PP + j * 16 + sg] = p;
+				Pw[i * (2 * NW) * PP + j * 16 + sg] = p;
 				ps += p;
 			}
 #pragma unroll
@@ -306,7 +306,7 @@ softmax_v_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_cons
 			float4 p[TI];
 #pragma unroll
 			for (int i = 0; i < TI; i++)
-				p[i] = *reinterpret_cast<const float4 *>(Pw + i * 16 * PP + s4 * 4);
+				p[i] = *reinterpret_cast<const float4 *>(Pw + i * (2 * NW) * PP + s4 * 4);
 #pragma unroll
 			for (int ss = 0; ss < 4; ss++) {
 				float vv[NV];
@@ -342,7 +342,7 @@ softmax_v_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_cons
 	const size_t vrow = size_t(sh.n_heads) * VW;
 #pragma unroll
 	for (int i = 0; i < TI; i++) {
-		const int t = t0 + i * 16 + tg;
+		const int t = t0 + i * (2 * NW) + tg;
 		if (t >= sh.n_tok)
 			continue;
 		const float inv = sh.mode == L1ATTN_SV_EXP ? 1.f : 1.f / lrow[i];
@@ -355,11 +355,11 @@ softmax_v_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_cons
 	}
 }
 
-template <int NV, int TI>
+template <int NV, int TI, int NW>
 int launch_tma(const float *q, const float *k, const float *v, float *vo, float *lse, int bs, int n_tok, int n_heads,
 	       int width, int mode, int nstage, size_t smem, cudaStream_t st)
 {
-	constexpr int TT = 16 * TI, VW = 16 * NV;
+	constexpr int TT = 2 * NW * TI, VW = 16 * NV, NTH = NW * 32;
 	const uint64_t dims[4] = {uint64_t(width), uint64_t(n_heads), uint64_t(n_tok), uint64_t(bs)};
 	const uint64_t str[3] = {uint64_t(width) * 4, uint64_t(n_heads) * width * 4, uint64_t(n_tok) * n_heads * width * 4};
 	const uint64_t vdims[4] = {uint64_t(VW), uint64_t(n_heads), uint64_t(n_tok), uint64_t(bs)};
@@ -384,7 +384,7 @@ int launch_tma(const float *q, const float *k, const float *v, float *vo, float 
 	const long long grid = (long long)bs * n_heads * sh.ntt;
 	if (grid > 0x7fffffffLL)
 		return L1ATTN_ERR_SHAPE;
-	auto kern = softmax_v_tma_kernel<NV, TI>;
+	auto kern = softmax_v_tma_kernel<NV, TI, NW>;
 	L1B_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
 	kern<<<unsigned(grid), NTH, smem, st>>>(qmap, kmap, vmap, vo, lse, sh, err);
 	L1B_LAUNCH_CHECK();
@@ -392,9 +392,9 @@ int launch_tma(const float *q, const float *k, const float *v, float *vo, float 
 }
 
 // shared memory of one CTA: query tile + ring + weight tile + alignment slack
-size_t sv_smem(int nwb, int nv, int ti, int nstage)
+size_t sv_smem(int nwb, int nv, int tt_rows, int nstage)
 {
-	const size_t tt = 16 * size_t(ti);
+	const size_t tt = size_t(tt_rows);
 	return size_t(nwb) * tt * 128 + size_t(nstage) * (size_t(nwb) * TS * 128 + size_t(TS) * nv * 64) + tt * PP * 4 + 1024;
 }
 
@@ -409,21 +409,28 @@ int softmax_v_tma(const float *q, const float *k, const float *v, float *vo, flo
 			return 1;
 	const int nwb = width / 32, nv = v_width / 16;
 	const size_t limit = 227 * 1024 - 256; // per-CTA maximum minus the static barriers
-	int ti = 0, nstage = 0;
-	for (int cand_ti : {8, 4}) {
+	// (rows per half-warp, warps): 4 x 16 and 8 x 8 give 128-row CTAs, 4 x 8 a 64-row CTA for the widest rows.
+	// Sixteen warps of 128 registers measured 7 % faster than eight of 168 (four warps per scheduler hide
+	// the shared-memory and arithmetic latencies); with 128 value columns the thread state does not fit 128 registers.
+	const bool nw16 = nv <= 4;
+	const int cand[2][2] = {{nw16 ? 4 : 8, nw16 ? 16 : 8}, {4, 8}};
+	int ti = 0, nw = 0, nstage = 0;
+	for (const auto &c : cand) {
 		for (int cand_ns : {3, 2})
-			if (!ti && sv_smem(nwb, nv, cand_ti, cand_ns) <= limit) {
-				ti = cand_ti;
+			if (!ti && sv_smem(nwb, nv, 2 * c[0] * c[1], cand_ns) <= limit) {
+				ti = c[0];
+				nw = c[1];
 				nstage = cand_ns;
 			}
 	}
 	if (!ti)
 		return 1;
-	const size_t smem = sv_smem(nwb, nv, ti, nstage);
-#define L1B_SV(NV_, TI_)                \
-	if (nv == NV_ && ti == TI_)     \
-		return launch_tma<NV_, TI_>(q, k, v, vo, lse, bs, n_tok, n_heads, width, mode, nstage, smem, st);
-	L1B_SV(2, 8) L1B_SV(4, 8) L1B_SV(8, 8) L1B_SV(2, 4) L1B_SV(4, 4) L1B_SV(8, 4)
+	const size_t smem = sv_smem(nwb, nv, 2 * ti * nw, nstage);
+#define L1B_SV(NV_, TI_, NW_)                       \
+	if (nv == NV_ && ti == TI_ && nw == NW_)    \
+		return launch_tma<NV_, TI_, NW_>(q, k, v, vo, lse, bs, n_tok, n_heads, width, mode, nstage, smem, st);
+	L1B_SV(2, 8, 8) L1B_SV(4, 8, 8) L1B_SV(8, 8, 8) L1B_SV(2, 4, 8) L1B_SV(4, 4, 8) L1B_SV(8, 4, 8)
+	L1B_SV(2, 4, 16) L1B_SV(4, 4, 16) L1B_SV(8, 4, 16)
 #undef L1B_SV
 	return 1;
 }
@@ -506,14 +513,15 @@ int launch_bwd_generic(const T *q, const T *k, const T *v, const T *dvo, const T
 // value rows stay in shared memory) and streams the query and dvo rows in tiles of 64; a half-warp
 // owns TI source rows, a lane 4 query columns for the scores and the <v, dvo> products, and NV value
 // columns for dv.  Every operand row is kept as 128-byte slices with the 128-byte swizzle.
-template <int NV, int TI>
-__global__ void __launch_bounds__(NTH, 1)
+template <int NV, int TI, int NW>
+__global__ void __launch_bounds__(NW * 32, 1)
 softmax_v_bwd_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kmap,
 			 const __grid_constant__ CUtensorMap vmap, const __grid_constant__ CUtensorMap gmap,
 			 const float *__restrict__ lse, const float *__restrict__ delta, float *__restrict__ dx,
 			 float *__restrict__ dv, SvShape sh, int *err)
 {
-	constexpr int TT = 16 * TI;
+	constexpr int TT = 2 * NW * TI; // source rows of the CTA
+	constexpr int NTH = NW * 32;
 	constexpr int VW = 16 * NV;
 	constexpr int NVB = VW / 32; // 128-byte slices per value row
 	extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -576,7 +584,7 @@ softmax_v_bwd_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_
 	const size_t hstride = size_t(sh.n_heads);
 
 	for (int m = 0; m < nt; m++) {
-		if (warp == (m & 7) && lane == 0 && m + sh.nstage - 1 < nt && !dead) {
+		if (warp == m % NW && lane == 0 && m + sh.nstage - 1 < nt && !dead) {
 			const int mm = m + sh.nstage - 1;
 			if (mbar_wait(&empty_bar[mm % sh.nstage], ((unsigned(mm) / unsigned(sh.nstage)) & 1u) ^ 1u, err))
 				load_tile(mm);
@@ -619,7 +627,7 @@ softmax_v_bwd_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_
 					qv[j] = Qb[(j * 16 + sg) * 8 + (c ^ (sg & 7))];
 #pragma unroll
 				for (int i = 0; i < TI; i++) {
-					const ulonglong2 kv = Kb[(i * 16 + tg) * 8 + (c ^ (tg & 7))];
+					const ulonglong2 kv = Kb[(i * (2 * NW) + tg) * 8 + (c ^ (tg & 7))];
 #pragma unroll
 					for (int j = 0; j < 4; j++) {
 						unsigned long long d0, d1;
@@ -648,7 +656,7 @@ softmax_v_bwd_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_
 					gv[j] = Gb[(j * 16 + sg) * 8 + (c ^ (sg & 7))];
 #pragma unroll
 				for (int i = 0; i < TI; i++) {
-					const float4 vv = Vb[(i * 16 + tg) * 8 + (c ^ (tg & 7))];
+					const float4 vv = Vb[(i * (2 * NW) + tg) * 8 + (c ^ (tg & 7))];
 #pragma unroll
 					for (int j = 0; j < 4; j++) {
 						dp[i][j] = fmaf(vv.x, gv[j].x, dp[i][j]);
@@ -663,13 +671,13 @@ softmax_v_bwd_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_
 		// weights, score gradients (stored), weights parked for the dv product
 #pragma unroll
 		for (int i = 0; i < TI; i++) {
-			const int s = s0 + i * 16 + tg;
+			const int s = s0 + i * (2 * NW) + tg;
 			float *dxr = dx + ((size_t(b) * sh.n_tok + (s < sh.n_tok ? s : 0)) * sh.n_tok) * hstride + h;
 #pragma unroll
 			for (int j = 0; j < 4; j++) {
 				const int t = m * TS + j * 16 + sg;
 				const float p = expf(acc[i][j] * sh.scale - lj[j]);
-				Pw[i * 16 * PP + j * 16 + sg] = p;
+				Pw[i * (2 * NW) * PP + j * 16 + sg] = p;
 				if (s < sh.n_tok && t < sh.n_tok)
 					dxr[size_t(t) * hstride] = p * (dp[i][j] - dj[j]);
 			}
@@ -682,7 +690,7 @@ softmax_v_bwd_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_
 			float4 p[TI];
 #pragma unroll
 			for (int i = 0; i < TI; i++)
-				p[i] = *reinterpret_cast<const float4 *>(Pw + i * 16 * PP + t4 * 4);
+				p[i] = *reinterpret_cast<const float4 *>(Pw + i * (2 * NW) * PP + t4 * 4);
 #pragma unroll
 			for (int tt = 0; tt < 4; tt++) {
 				const int trow = t4 * 4 + tt;
@@ -720,7 +728,7 @@ softmax_v_bwd_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_
 	const size_t vrow = size_t(sh.n_heads) * VW;
 #pragma unroll
 	for (int i = 0; i < TI; i++) {
-		const int s = s0 + i * 16 + tg;
+		const int s = s0 + i * (2 * NW) + tg;
 		if (s >= sh.n_tok)
 			continue;
 		float *op = dv + (size_t(b) * sh.n_tok + s) * vrow + size_t(h) * VW + sg * NV;
@@ -730,17 +738,17 @@ softmax_v_bwd_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_
 	}
 }
 
-size_t sv_bwd_smem(int nwb, int nv, int ti, int nstage)
+size_t sv_bwd_smem(int nwb, int nv, int tt_rows, int nstage)
 {
-	const size_t tt = 16 * size_t(ti), nvb = size_t(nv) / 2;
+	const size_t tt = size_t(tt_rows), nvb = size_t(nv) / 2;
 	return (size_t(nwb) + nvb) * tt * 128 + size_t(nstage) * (size_t(nwb) + nvb) * TS * 128 + tt * PP * 4 + 1024;
 }
 
-template <int NV, int TI>
+template <int NV, int TI, int NW>
 int launch_bwd_tma(const float *q, const float *k, const float *v, const float *dvo, const float *lse, const float *delta,
 		   float *dx, float *dv, int bs, int n_tok, int n_heads, int width, int nstage, size_t smem, cudaStream_t st)
 {
-	constexpr int TT = 16 * TI, VW = 16 * NV;
+	constexpr int TT = 2 * NW * TI, VW = 16 * NV, NTH = NW * 32;
 	const uint64_t dims[4] = {uint64_t(width), uint64_t(n_heads), uint64_t(n_tok), uint64_t(bs)};
 	const uint64_t str[3] = {uint64_t(width) * 4, uint64_t(n_heads) * width * 4, uint64_t(n_tok) * n_heads * width * 4};
 	const uint64_t vdims[4] = {uint64_t(VW), uint64_t(n_heads), uint64_t(n_tok), uint64_t(bs)};
@@ -766,7 +774,7 @@ int launch_bwd_tma(const float *q, const float *k, const float *v, const float *
 	const long long grid = (long long)bs * n_heads * sh.ntt;
 	if (grid > 0x7fffffffLL)
 		return L1ATTN_ERR_SHAPE;
-	auto kern = softmax_v_bwd_tma_kernel<NV, TI>;
+	auto kern = softmax_v_bwd_tma_kernel<NV, TI, NW>;
 	L1B_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
 	kern<<<unsigned(grid), NTH, smem, st>>>(qmap, kmap, vmap, gmap, lse, delta, dx, dv, sh, err);
 	L1B_LAUNCH_CHECK();
@@ -783,21 +791,25 @@ int softmax_v_bwd_tma(const float *q, const float *k, const float *v, const floa
 			return 1;
 	const int nwb = width / 32, nv = v_width / 16;
 	const size_t limit = 227 * 1024 - 256;
-	int ti = 0, nstage = 0;
-	for (int cand_ti : {8, 4}) {
+	const bool nw16 = nv <= 4; // see softmax_v_tma
+	const int cand[2][2] = {{nw16 ? 4 : 8, nw16 ? 16 : 8}, {4, 8}};
+	int ti = 0, nw = 0, nstage = 0;
+	for (const auto &c : cand) {
 		for (int cand_ns : {3, 2})
-			if (!ti && sv_bwd_smem(nwb, nv, cand_ti, cand_ns) <= limit) {
-				ti = cand_ti;
+			if (!ti && sv_bwd_smem(nwb, nv, 2 * c[0] * c[1], cand_ns) <= limit) {
+				ti = c[0];
+				nw = c[1];
 				nstage = cand_ns;
 			}
 	}
 	if (!ti)
 		return 1;
-	const size_t smem = sv_bwd_smem(nwb, nv, ti, nstage);
-#define L1B_SVB(NV_, TI_)               \
-	if (nv == NV_ && ti == TI_)     \
-		return launch_bwd_tma<NV_, TI_>(q, k, v, dvo, lse, delta, dx, dv, bs, n_tok, n_heads, width, nstage, smem, st);
-	L1B_SVB(2, 8) L1B_SVB(4, 8) L1B_SVB(8, 8) L1B_SVB(2, 4) L1B_SVB(4, 4) L1B_SVB(8, 4)
+	const size_t smem = sv_bwd_smem(nwb, nv, 2 * ti * nw, nstage);
+#define L1B_SVB(NV_, TI_, NW_)                      \
+	if (nv == NV_ && ti == TI_ && nw == NW_)    \
+		return launch_bwd_tma<NV_, TI_, NW_>(q, k, v, dvo, lse, delta, dx, dv, bs, n_tok, n_heads, width, nstage, smem, st);
+	L1B_SVB(2, 8, 8) L1B_SVB(4, 8, 8) L1B_SVB(8, 8, 8) L1B_SVB(2, 4, 8) L1B_SVB(4, 4, 8) L1B_SVB(8, 4, 8)
+	L1B_SVB(2, 4, 16) L1B_SVB(4, 4, 16) L1B_SVB(8, 4, 16)
 #undef L1B_SVB
 	return 1;
 }
