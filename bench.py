@@ -333,6 +333,40 @@ def run_train(args, wl):
         losses.append(float(loss))
         return e0.elapsed_time(e1) / steps, losses
 
+    def timed_graph(attn_fn, steps, warmup):
+        """The same step captured once into a CUDA graph and replayed (whole-network capture: forward,
+        backward and the AdamW update; static input tensors).  Works because the operators launch on the
+        current stream, take their edge index from the prebuilt graph object and never synchronise."""
+        model = build_transformer(wl, attn_fn, dev)
+        opt = torch.optim.AdamW(model.parameters(), lr=1e-3, capturable=True)
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(3):
+                opt.zero_grad(set_to_none=True)
+                F.cross_entropy(model(tokens).reshape(-1, wl["vocab"]), targets.reshape(-1)).backward()
+                opt.step()
+        torch.cuda.current_stream().wait_stream(side)
+        g = torch.cuda.CUDAGraph()
+        opt.zero_grad(set_to_none=True)
+        with torch.cuda.graph(g):
+            loss = F.cross_entropy(model(tokens).reshape(-1, wl["vocab"]), targets.reshape(-1))
+            loss.backward()
+            opt.step()
+        losses = []
+        for _ in range(max(warmup, 3)):
+            g.replay()
+            losses.append(float(loss))
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        losses.append(float(loss))
+        return e0.elapsed_time(e1) / steps, losses
+
     ours = lambda vf, vb, q, k: graph.attend_bidi(vf, vb, q, k)
     ms, losses = timed(ours, args.steps, args.warmup)
     line = {"metric": "training tokens/s, 4-layer pre-LN transformer with L1AttnSparseBidi (config 5)",
@@ -342,6 +376,10 @@ def run_train(args, wl):
             "config": {"workload": "train_cfg5", **{k: v for k, v in wl.items() if k != "kind"},
                        "edges": int(graph.n_edges), "dst_mxlen": int(graph.dst_mxlen), "optimizer": "AdamW"},
             "loss_first": losses[0], "loss_last": losses[-1]}
+    if args.cuda_graph:
+        gms, gl = timed_graph(ours, args.steps, args.warmup)
+        line["cuda_graph"] = {"ms_per_step": gms, "tokens_per_s": wl["batch"] * n / (gms * 1e-3), "loss_last": gl[-1],
+                              "note": "one captured graph per step (forward, backward, AdamW), replayed"}
     if args.compare_reference_cuda:
         refdir = os.path.join(ROOT, "oracle", "_ref")
         if os.path.exists(os.path.join(refdir, "ref_l1attn_sparse_bidi_cuda_drv.so")):
@@ -649,6 +687,8 @@ def main():
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
                     help="weak (default): every rank runs the full workload on its own data; strong: the "
                          "workload's batch is split across the ranks")
+    ap.add_argument("--cuda-graph", action="store_true",
+                    help="train_cfg5: also time the step captured into one CUDA graph and replayed")
     ap.add_argument("--kernel-only", action="store_true", help="skip the end-to-end and CPU legs (profiling runs)")
     args = ap.parse_args()
     wl = WORKLOADS[args.workload]
