@@ -322,7 +322,7 @@ def run_train(args, wl):
             return loss
 
         for _ in range(max(warmup, 3)):
-            losses.append(float(step()))
+            losses.append(float(step().detach()))
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
@@ -330,7 +330,7 @@ def run_train(args, wl):
             loss = step()
         e1.record()
         torch.cuda.synchronize()
-        losses.append(float(loss))
+        losses.append(float(loss.detach()))
         return e0.elapsed_time(e1) / steps, losses
 
     def timed_graph(attn_fn, steps, warmup):
@@ -356,7 +356,7 @@ def run_train(args, wl):
         losses = []
         for _ in range(max(warmup, 3)):
             g.replay()
-            losses.append(float(loss))
+            losses.append(float(loss.detach()))
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
@@ -364,7 +364,7 @@ def run_train(args, wl):
             g.replay()
         e1.record()
         torch.cuda.synchronize()
-        losses.append(float(loss))
+        losses.append(float(loss.detach()))
         return e0.elapsed_time(e1) / steps, losses
 
     ours = lambda vf, vb, q, k: graph.attend_bidi(vf, vb, q, k)

@@ -46,6 +46,8 @@ extern "C" {
 
 #define L1ATTN_F32 0
 #define L1ATTN_F64 1
+#define L1ATTN_F16 2  /* IEEE half storage, float arithmetic: l1attn_sparse_fwd only */
+#define L1ATTN_BF16 3 /* bfloat16 storage, float arithmetic: l1attn_sparse_fwd only */
 
 /* normalisation of l1attn_dense_softmax_v_fwd */
 #define L1ATTN_SV_SOFTMAX 0          /* softmax over the source tokens (F.softmax(attn, 1)) */
@@ -150,6 +152,9 @@ int l1attn_sparse_build_index(const int32_t *coo, int cl, int n_tok, int dst_mxl
  * Replaces l1attn_sparse_cuda_drv.forward (cuda/l1attn_sparse_cuda_drv.cpp:32-46,
  * cuda/l1attn_sparse_cuda_kernel.cu:373-445) and l1attn_sparse_bidi_cuda_drv.forward
  * (cuda/l1attn_sparse_bidi_cuda_drv.cpp:34-50, cuda/l1attn_sparse_cuda_kernel.cu:651-725).
+ * dtype may also be L1ATTN_F16 / L1ATTN_BF16 here (and only here): v, vb, q, k, vo, attn are then
+ * 16-bit tensors, the arithmetic is float; the reference dispatches Half in its sparse forward only
+ * (cuda/l1attn_sparse_cuda_kernel.cu:405, :483).
  */
 int l1attn_sparse_fwd(const void *v, const void *vb, const void *q, const void *k,
 		      const void *index, void *vo, void *attn,

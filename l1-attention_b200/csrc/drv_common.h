@@ -13,13 +13,20 @@
 	CHECK_CUDA(x);  \
 	CHECK_CONTIGUOUS(x)
 
-inline int l1b_dtype(const torch::Tensor &t, const char *what)
+// allow16: the sparse forward also takes float16 / bfloat16 storage (the reference dispatches Half
+// there, cuda/l1attn_sparse_cuda_kernel.cu:405); every other operator is float32 / float64 only
+inline int l1b_dtype(const torch::Tensor &t, const char *what, bool allow16 = false)
 {
 	if (t.scalar_type() == torch::kFloat32)
 		return L1ATTN_F32;
 	if (t.scalar_type() == torch::kFloat64)
 		return L1ATTN_F64;
-	TORCH_CHECK(false, what, ": expected float32 or float64 tensors, got ", t.scalar_type());
+	if (allow16 && t.scalar_type() == torch::kFloat16)
+		return L1ATTN_F16;
+	if (allow16 && t.scalar_type() == torch::kBFloat16)
+		return L1ATTN_BF16;
+	TORCH_CHECK(false, what, ": expected float32 or float64 tensors", allow16 ? " (or float16 / bfloat16)" : "", ", got ",
+		    t.scalar_type());
 	return -1;
 }
 

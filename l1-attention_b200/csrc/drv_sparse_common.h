@@ -68,7 +68,7 @@ inline std::vector<torch::Tensor> l1b_sparse_forward(torch::Tensor v, torch::Ten
 		l1b_same(v, vb, "vf", "vb");
 	l1b_check_coo(coo, q);
 	TORCH_CHECK(dst_mxlen >= 0, "dst_mxlen must be >= 0");
-	const int dt = l1b_dtype(q, "l1attnSparse forward");
+	const int dt = l1b_dtype(q, "l1attnSparse forward", true);
 	const c10::cuda::CUDAGuard guard(q.device());
 	const int bs = q.size(0), n = q.size(1), h = q.size(2), w = q.size(3), wv = v.size(3), cl = coo.size(0);
 	auto index = l1b_index_for(coo, n, dst_mxlen);

@@ -8,7 +8,10 @@
 // accumulating in registers and storing once.  No atomics, fixed summation order, results are
 // bit-reproducible.  Within a warp LPH lanes share a head and split its width; a head's dot
 // products / L1 sums are finished with xor-shuffles.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <initializer_list>
+#include <type_traits>
 #include <mutex>
 #include "common.cuh"
 
@@ -33,6 +36,55 @@ template <typename T, int VEC> __device__ __forceinline__ Pack<T, VEC> ldv(const
 			r.v[e] = T(0);
 	}
 	return r;
+}
+
+// Storage type S, arithmetic type T.  S == T for float and double; for the 16-bit storage types
+// (__half, __nv_bfloat16) the forward loads VEC elements at once, computes in float and rounds on store.
+template <typename S> __device__ __forceinline__ float to_f(S x) { return float(x); }
+template <> __device__ __forceinline__ float to_f<__half>(__half x) { return __half2float(x); }
+template <> __device__ __forceinline__ float to_f<__nv_bfloat16>(__nv_bfloat16 x) { return __bfloat162float(x); }
+template <typename S> __device__ __forceinline__ S from_f(float x) { return S(x); }
+template <> __device__ __forceinline__ __half from_f<__half>(float x) { return __float2half_rn(x); }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
+
+template <typename S, typename T, int VEC> __device__ __forceinline__ Pack<T, VEC> ldc(const S *p, bool ok)
+{
+	if constexpr (std::is_same<S, T>::value) {
+		return ldv<T, VEC>(p, ok);
+	} else {
+		const Pack<S, VEC> raw = ldv<S, VEC>(p, ok);
+		Pack<T, VEC> r;
+#pragma unroll
+		for (int e = 0; e < VEC; e++)
+			r.v[e] = to_f<S>(raw.v[e]);
+		return r;
+	}
+}
+template <typename S, typename T, int VEC> __device__ __forceinline__ void stc(S *p, const Pack<T, VEC> &x)
+{
+	if constexpr (std::is_same<S, T>::value) {
+		*reinterpret_cast<Pack<T, VEC> *>(p) = x;
+	} else {
+		Pack<S, VEC> raw;
+#pragma unroll
+		for (int e = 0; e < VEC; e++)
+			raw.v[e] = from_f<S>(x.v[e]);
+		*reinterpret_cast<Pack<S, VEC> *>(p) = raw;
+	}
+}
+template <typename S, typename T> __device__ __forceinline__ T ld1(const S *p)
+{
+	if constexpr (std::is_same<S, T>::value)
+		return *p;
+	else
+		return to_f<S>(*p);
+}
+template <typename S, typename T> __device__ __forceinline__ void st1(S *p, T x)
+{
+	if constexpr (std::is_same<S, T>::value)
+		*p = x;
+	else
+		*p = from_f<S>(x);
 }
 
 // LPHC > 0: lanes per head known at compile time (the shuffles unroll, index math folds); 0: run-time value
@@ -83,10 +135,10 @@ constexpr int U = 4;
 #define L1B_XLOOP(WIDTH) _Pragma("unroll") for (int it_ = 0, x = w.li * VEC; (NX > 0 ? it_ < NX : x < (WIDTH)); it_++, x += step)
 
 // ---- forward, dst pass: scores -> exp -> (+1)-softmax -> attn, vo[dst] = sum_r a_r v[src_r] ----
-template <typename T, int VEC, int LPHC, int NX>
-__global__ void __launch_bounds__(256) sparse_fwd_dst_kernel(SparseArgs a, const T *__restrict__ v,
-							      const T *__restrict__ q, const T *__restrict__ k,
-							      T *__restrict__ vo, T *attn, T scale)
+template <typename S, typename T, int VEC, int LPHC, int NX>
+__global__ void __launch_bounds__(256) sparse_fwd_dst_kernel(SparseArgs a, const S *__restrict__ v,
+							      const S *__restrict__ q, const S *__restrict__ k,
+							      S *__restrict__ vo, S *attn, T scale)
 {
 	Who w;
 	if (!decode<LPHC>(a, w))
@@ -94,8 +146,8 @@ __global__ void __launch_bounds__(256) sparse_fwd_dst_kernel(SparseArgs a, const
 	const int dst = w.tok, H = a.n_heads, W = a.width, Wv = a.v_width, dm = a.dm;
 	const int hh = w.head_ok ? w.h : 0;
 	const size_t tokrow = size_t(w.b) * a.n_tok;
-	const T *qrow = q + ((tokrow + dst) * H + hh) * W;
-	T *arow = attn + ((tokrow + dst) * dm) * H + hh;
+	const S *qrow = q + ((tokrow + dst) * H + hh) * W;
+	S *arow = attn + ((tokrow + dst) * dm) * H + hh;
 	const int32_t *slots = a.slot_src + size_t(dst) * dm;
 	const int lph = LPHC > 0 ? LPHC : a.lph;
 	const int step = lph * VEC;
@@ -110,11 +162,11 @@ __global__ void __launch_bounds__(256) sparse_fwd_dst_kernel(SparseArgs a, const
 			part[u] = T(0);
 		}
 		L1B_XLOOP(W) {
-			const Pack<T, VEC> qv = ldv<T, VEC>(qrow + x, w.head_ok);
+			const Pack<T, VEC> qv = ldc<S, T, VEC>(qrow + x, w.head_ok);
 			Pack<T, VEC> kv[U];
 #pragma unroll
 			for (int u = 0; u < U; u++)
-				kv[u] = ldv<T, VEC>(k + ((tokrow + (src[u] < 0 ? 0 : src[u])) * H + hh) * W + x,
+				kv[u] = ldc<S, T, VEC>(k + ((tokrow + (src[u] < 0 ? 0 : src[u])) * H + hh) * W + x,
 						    w.head_ok && src[u] >= 0);
 #pragma unroll
 			for (int u = 0; u < U; u++)
@@ -130,16 +182,16 @@ __global__ void __launch_bounds__(256) sparse_fwd_dst_kernel(SparseArgs a, const
 			const T e = src[u] >= 0 ? exp_t(part[u] * scale) : T(0);
 			denom += e;
 			if (w.li == 0 && w.head_ok && r0 + u < dm)
-				arow[size_t(r0 + u) * H] = e;
+				st1<S, T>(arow + size_t(r0 + u) * H, e);
 		}
 	}
 	__syncwarp();
 	if (a.use_softmax && w.head_ok)
 		for (int r = w.li; r < dm; r += lph)
-			arow[size_t(r) * H] = arow[size_t(r) * H] / denom;
+			st1<S, T>(arow + size_t(r) * H, ld1<S, T>(arow + size_t(r) * H) / denom);
 	__syncwarp();
 
-	T *orow = vo + ((tokrow + dst) * H + hh) * Wv;
+	S *orow = vo + ((tokrow + dst) * H + hh) * Wv;
 	L1B_XLOOP(Wv) {
 		Pack<T, VEC> acc = ldv<T, VEC>(nullptr, false);
 		for (int r0 = 0; r0 < dm; r0 += U) {
@@ -149,8 +201,8 @@ __global__ void __launch_bounds__(256) sparse_fwd_dst_kernel(SparseArgs a, const
 			for (int u = 0; u < U; u++) {
 				const int src = r0 + u < dm ? slots[r0 + u] : -1;
 				const bool ok = w.head_ok && src >= 0;
-				ar[u] = ok ? arow[size_t(r0 + u) * H] : T(0);
-				vv[u] = ldv<T, VEC>(v + ((tokrow + (src < 0 ? 0 : src)) * H + hh) * Wv + x, ok);
+				ar[u] = ok ? ld1<S, T>(arow + size_t(r0 + u) * H) : T(0);
+				vv[u] = ldc<S, T, VEC>(v + ((tokrow + (src < 0 ? 0 : src)) * H + hh) * Wv + x, ok);
 			}
 #pragma unroll
 			for (int u = 0; u < U; u++)
@@ -159,14 +211,14 @@ __global__ void __launch_bounds__(256) sparse_fwd_dst_kernel(SparseArgs a, const
 					acc.v[i] += ar[u] * vv[u].v[i];
 		}
 		if (w.head_ok)
-			*reinterpret_cast<Pack<T, VEC> *>(orow + x) = acc;
+			stc<S, T, VEC>(orow + x, acc);
 	}
 }
 
 // ---- forward, src pass (bidi only): vo[src] += sum_{incoming (dst,r)} a[dst][r] * vb[dst] ----
-template <typename T, int VEC, int LPHC, int NX>
-__global__ void __launch_bounds__(256) sparse_fwd_src_kernel(SparseArgs a, const T *__restrict__ vb,
-							      const T *__restrict__ attn, T *vo)
+template <typename S, typename T, int VEC, int LPHC, int NX>
+__global__ void __launch_bounds__(256) sparse_fwd_src_kernel(SparseArgs a, const S *__restrict__ vb,
+							      const S *__restrict__ attn, S *vo)
 {
 	Who w;
 	if (!decode<LPHC>(a, w))
@@ -178,7 +230,7 @@ __global__ void __launch_bounds__(256) sparse_fwd_src_kernel(SparseArgs a, const
 	const int e0 = a.csc_off[src], e1 = a.csc_off[src + 1];
 	const int lph = LPHC > 0 ? LPHC : a.lph;
 	const int step = lph * VEC;
-	T *orow = vo + ((tokrow + src) * H + w.h) * Wv;
+	S *orow = vo + ((tokrow + src) * H + w.h) * Wv;
 	L1B_XLOOP(Wv) {
 		Pack<T, VEC> acc = ldv<T, VEC>(nullptr, false);
 		for (int eb = e0; eb < e1; eb += U) {
@@ -188,8 +240,8 @@ __global__ void __launch_bounds__(256) sparse_fwd_src_kernel(SparseArgs a, const
 			for (int u = 0; u < U; u++) {
 				const bool ok = eb + u < e1;
 				const int slot = ok ? a.csc_slot[eb + u] : 0;
-				ar[u] = ok ? attn[(tokrow * dm + slot) * H + w.h] : T(0);
-				vv[u] = ldv<T, VEC>(vb + ((tokrow + slot / dm) * H + w.h) * Wv + x, ok);
+				ar[u] = ok ? ld1<S, T>(attn + (tokrow * dm + slot) * H + w.h) : T(0);
+				vv[u] = ldc<S, T, VEC>(vb + ((tokrow + slot / dm) * H + w.h) * Wv + x, ok);
 			}
 #pragma unroll
 			for (int u = 0; u < U; u++)
@@ -197,11 +249,11 @@ __global__ void __launch_bounds__(256) sparse_fwd_src_kernel(SparseArgs a, const
 				for (int i = 0; i < VEC; i++)
 					acc.v[i] += ar[u] * vv[u].v[i];
 		}
-		Pack<T, VEC> cur = ldv<T, VEC>(orow + x, true);
+		Pack<T, VEC> cur = ldc<S, T, VEC>(orow + x, true);
 #pragma unroll
 		for (int i = 0; i < VEC; i++)
 			cur.v[i] += acc.v[i];
-		*reinterpret_cast<Pack<T, VEC> *>(orow + x) = cur;
+		stc<S, T, VEC>(orow + x, cur);
 	}
 }
 
@@ -430,8 +482,8 @@ Grid grid_for(const SparseArgs &a)
 	return {unsigned(blocks), blocks <= 0x7fffffffLL};
 }
 
-template <typename T, int VEC>
-int fwd_t(SparseArgs a, const T *v, const T *vb, const T *q, const T *k, T *vo, T *attn, cudaStream_t st)
+template <typename S, typename T, int VEC>
+int fwd_t(SparseArgs a, const S *v, const S *vb, const S *q, const S *k, S *vo, S *attn, cudaStream_t st)
 {
 	const int mw = a.width > a.v_width ? a.width : a.v_width;
 	a.lph = pow2_ceil((mw + 4 * VEC - 1) / (4 * VEC)); // four 16-byte vectors per lane: fewer shuffle rounds and less index math per term
@@ -444,10 +496,10 @@ int fwd_t(SparseArgs a, const T *v, const T *vb, const T *q, const T *k, T *vo, 
 	// lanes per head as a compile-time constant for the common widths (16-byte vectors, 32..128+ columns)
 #define L1B_FWD(LP, NXV)                                                                                      \
 	do {                                                                                             \
-		sparse_fwd_dst_kernel<T, VEC, LP, NXV><<<g.blocks, 256, 0, st>>>(a, v, q, k, vo, attn, scale); \
+		sparse_fwd_dst_kernel<S, T, VEC, LP, NXV><<<g.blocks, 256, 0, st>>>(a, v, q, k, vo, attn, scale); \
 		L1B_LAUNCH_CHECK();                                                                      \
 		if (a.bidi) {                                                                            \
-			sparse_fwd_src_kernel<T, VEC, LP, NXV><<<g.blocks, 256, 0, st>>>(a, vb, attn, vo);     \
+			sparse_fwd_src_kernel<S, T, VEC, LP, NXV><<<g.blocks, 256, 0, st>>>(a, vb, attn, vo);     \
 			L1B_LAUNCH_CHECK();                                                              \
 		}                                                                                        \
 	} while (0)
@@ -539,11 +591,13 @@ extern "C" size_t l1attn_sparse_bwd_scratch_bytes(int bs, int n_tok, int n_heads
 	return n ? n : 16;
 }
 
-static int check_sparse(int bs, int n_tok, int n_heads, int width, int v_width, int cl, int dst_mxlen, int dtype)
+static int check_sparse(int bs, int n_tok, int n_heads, int width, int v_width, int cl, int dst_mxlen, int dtype,
+			bool allow16 = false)
 {
 	if (bs < 0 || n_tok < 0 || n_heads < 0 || width < 1 || v_width < 1 || cl < 0 || dst_mxlen < 0)
 		return L1ATTN_ERR_ARG;
-	if (dtype != L1ATTN_F32 && dtype != L1ATTN_F64)
+	const bool is16 = dtype == L1ATTN_F16 || dtype == L1ATTN_BF16;
+	if (dtype != L1ATTN_F32 && dtype != L1ATTN_F64 && !(allow16 && is16))
 		return L1ATTN_ERR_ARG;
 	if ((long long)n_tok * dst_mxlen > 0x7fffffffLL)
 		return L1ATTN_ERR_SHAPE;
@@ -554,14 +608,14 @@ extern "C" int l1attn_sparse_fwd(const void *v, const void *vb, const void *q, c
 				  void *vo, void *attn, int bs, int n_tok, int n_heads, int width, int v_width, int cl,
 				  int dst_mxlen, int use_softmax, int bidi, int dtype, void *stream)
 {
-	int rc = check_sparse(bs, n_tok, n_heads, width, v_width, cl, dst_mxlen, dtype);
+	int rc = check_sparse(bs, n_tok, n_heads, width, v_width, cl, dst_mxlen, dtype, true);
 	if (rc)
 		return rc;
 	if (bs == 0 || n_tok == 0 || n_heads == 0)
 		return L1ATTN_OK;
 	if (!v || !q || !k || !index || !vo || !attn || (bidi && !vb))
 		return L1ATTN_ERR_ARG;
-	const size_t es = dtype == L1ATTN_F64 ? 8 : 4;
+	const size_t es = dtype == L1ATTN_F64 ? 8 : dtype == L1ATTN_F32 ? 4 : 2;
 	for (const void *p : {v, vb, q, k, (const void *)vo, (const void *)attn})
 		if (p && !aligned(p, es))
 			return L1ATTN_ERR_ALIGN;
@@ -570,17 +624,33 @@ extern "C" int l1attn_sparse_fwd(const void *v, const void *vb, const void *q, c
 	SparseArgs a{bs, n_tok, n_heads, width, v_width, dst_mxlen, 32, use_softmax != 0, bidi != 0,
 		     ix.slot_src, ix.csc_off, ix.csc_slot};
 	const bool a16 = all_aligned16({v, vb, q, k, vo});
+	if (dtype == L1ATTN_F16 || dtype == L1ATTN_BF16) {
+		// 16-bit storage, float arithmetic: four elements (8 bytes) per load when rows allow it
+		bool a8 = width % 4 == 0 && v_width % 4 == 0;
+		for (const void *p : {v, vb, q, k, (const void *)vo})
+			a8 = a8 && (!p || aligned(p, 8));
+		if (dtype == L1ATTN_F16) {
+			using H = __half;
+			if (a8)
+				return fwd_t<H, float, 4>(a, (const H *)v, (const H *)vb, (const H *)q, (const H *)k, (H *)vo, (H *)attn, st);
+			return fwd_t<H, float, 1>(a, (const H *)v, (const H *)vb, (const H *)q, (const H *)k, (H *)vo, (H *)attn, st);
+		}
+		using B = __nv_bfloat16;
+		if (a8)
+			return fwd_t<B, float, 4>(a, (const B *)v, (const B *)vb, (const B *)q, (const B *)k, (B *)vo, (B *)attn, st);
+		return fwd_t<B, float, 1>(a, (const B *)v, (const B *)vb, (const B *)q, (const B *)k, (B *)vo, (B *)attn, st);
+	}
 	if (dtype == L1ATTN_F32) {
 		if (a16 && width % 4 == 0 && v_width % 4 == 0)
-			return fwd_t<float, 4>(a, (const float *)v, (const float *)vb, (const float *)q, (const float *)k,
+			return fwd_t<float, float, 4>(a, (const float *)v, (const float *)vb, (const float *)q, (const float *)k,
 					       (float *)vo, (float *)attn, st);
-		return fwd_t<float, 1>(a, (const float *)v, (const float *)vb, (const float *)q, (const float *)k,
+		return fwd_t<float, float, 1>(a, (const float *)v, (const float *)vb, (const float *)q, (const float *)k,
 				       (float *)vo, (float *)attn, st);
 	}
 	if (a16 && width % 2 == 0 && v_width % 2 == 0)
-		return fwd_t<double, 2>(a, (const double *)v, (const double *)vb, (const double *)q, (const double *)k,
+		return fwd_t<double, double, 2>(a, (const double *)v, (const double *)vb, (const double *)q, (const double *)k,
 					(double *)vo, (double *)attn, st);
-	return fwd_t<double, 1>(a, (const double *)v, (const double *)vb, (const double *)q, (const double *)k,
+	return fwd_t<double, double, 1>(a, (const double *)v, (const double *)vb, (const double *)q, (const double *)k,
 				(double *)vo, (double *)attn, st);
 }
 

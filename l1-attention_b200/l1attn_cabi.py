@@ -15,7 +15,7 @@ import numpy as np
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libl1attn_b200.so")
-F32, F64 = 0, 1
+F32, F64, F16, BF16 = 0, 1, 2, 3  # F16 / BF16: storage types of the sparse forward only
 
 _c = ctypes
 _vp, _i, _ll, _sz = _c.c_void_p, _c.c_int, _c.c_longlong, _c.c_size_t
@@ -174,12 +174,16 @@ def expand_coo_host(co):
 
 # ------------------------------------------------------------------ device (torch) helpers
 
-def _tdt(t):
+def _tdt(t, allow16=False):
     import torch
     if t.dtype == torch.float32:
         return F32
     if t.dtype == torch.float64:
         return F64
+    if allow16 and t.dtype == torch.float16:
+        return F16
+    if allow16 and t.dtype == torch.bfloat16:
+        return BF16
     raise TypeError("float32 or float64 expected, got %s" % t.dtype)
 
 
@@ -270,7 +274,7 @@ def sparse_fwd(v, q, k, index, use_softmax=True, vb=None, out=None):
         vo, attn = out
     _check(lib().l1attn_sparse_fwd(_dp(v), _dp(vb), _dp(q), _dp(k), _dp(index.buf), _dp(vo), _dp(attn), bs, n, h, w,
                                    wv, index.cl, index.dst_mxlen, int(bool(use_softmax)), int(vb is not None),
-                                   _tdt(q), _stream()), "l1attn_sparse_fwd")
+                                   _tdt(q, allow16=True), _stream()), "l1attn_sparse_fwd")
     return vo, attn
 
 

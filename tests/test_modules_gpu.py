@@ -157,7 +157,7 @@ def test_training_steps_match_a_pure_torch_model():
             loss = F.cross_entropy(model(tokens).reshape(-1, wl["vocab"]), targets.reshape(-1))
             loss.backward()
             opt.step()
-            losses.append(float(loss))
+            losses.append(float(loss.detach()))
         curves.append(losses)
     assert curves[0][-1] < curves[0][0]
     assert np.allclose(curves[0], curves[1], rtol=2e-4), curves

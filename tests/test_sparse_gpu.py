@@ -88,6 +88,55 @@ def test_vs_oracle(case, usm, bidi, dtype):
         assert_close(x, r, tol, name)
 
 
+@pytest.mark.parametrize("tdtype", ["float16", "bfloat16"])
+@pytest.mark.parametrize("bidi", [False, True])
+@pytest.mark.parametrize("usm", [True, False])
+@pytest.mark.parametrize("case", CASES)
+def test_forward_16bit_storage(case, usm, bidi, tdtype):
+    """float16 / bfloat16 tensors in the forward (the reference dispatches Half there,
+    cuda/l1attn_sparse_cuda_kernel.cu:405): storage is 16-bit, arithmetic float, so the result is the
+    float64 oracle on the same (16-bit representable) inputs up to the rounding of the outputs:
+    2^-11 relative for float16, 2^-8 for bfloat16, plus the same rounding of the stored weights."""
+    from oracle import oracle
+    cabi = _cabi()
+    tdt = getattr(torch, tdtype)
+    bs, n, h, w, wv, deg = case
+    rng = np.random.RandomState(sum(case) + 5 * usm + 3 * bidi)
+    co = random_graph(rng, n, deg)
+    coo, dm, _ = oracle.expand_coo(co)
+    mk = lambda shape, sc: (sc * torch.from_numpy(rng.standard_normal(shape))).to(tdt).cuda()
+    q, k = mk((bs, n, h, w), 0.3), mk((bs, n, h, w), 0.3)
+    v, vb = mk((bs, n, h, wv), 1.0), (mk((bs, n, h, wv), 1.0) if bidi else None)
+    ix = cabi.SparseIndex(_dev(coo.astype(np.int32)), n, dm)
+    vo, attn = cabi.sparse_fwd(v, q, k, ix, usm, vb=vb)
+    assert vo.dtype == tdt and attn.dtype == tdt
+    f64 = lambda t: None if t is None else t.double().cpu().numpy()
+    if bidi:
+        rvo, rattn = oracle.sparse_bidi_fwd(f64(v), f64(vb), f64(q), f64(k), coo, dm, usm)
+    else:
+        rvo, rattn = oracle.sparse_fwd(f64(v), f64(q), f64(k), coo, dm, usm)
+    tol = 2e-3 if tdtype == "float16" else 1.6e-2
+    assert_close(f64(vo), rvo, tol, "vo " + tdtype)
+    assert_close(f64(attn), rattn, tol, "attn " + tdtype)
+
+
+def test_16bit_module_forward_and_backward_error():
+    """Through the module: float16 forward works, backward is refused as in the reference (whose backward
+    dispatches float32 / float64 only, cuda/l1attn_sparse_cuda_kernel.cu:483)."""
+    import l1attn_sparse_cuda
+    co = torch.tensor([[0, 0], [0, 1], [1, 0], [2, 2], [2, 1]])
+    coo, dm, _ = l1attn_sparse_cuda.expandCoo(co)
+    v, q, k = (torch.randn(1, 3, 2, 32, device="cuda", dtype=torch.float16, requires_grad=True) for _ in range(3))
+    vo = l1attn_sparse_cuda.L1AttnSparse()(v, q, k, coo.cuda(), dm, True)
+    assert vo.dtype == torch.float16 and bool(torch.isfinite(vo).all())
+    with pytest.raises(RuntimeError, match="float32 or float64"):
+        vo.sum().backward()
+    # the dense operator does not take 16-bit tensors at all
+    import l1attn_cuda
+    with pytest.raises(RuntimeError, match="float32 or float64"):
+        l1attn_cuda.L1Attn()(q, k)
+
+
 @pytest.mark.parametrize("usm", [1, 0])
 def test_golden_fixtures(golden, usm):
     g = golden["sparse"]
