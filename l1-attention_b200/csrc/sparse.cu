@@ -134,6 +134,58 @@ constexpr int U = 4;
 // is a compile-time constant (width == NX * lanes-per-head * VEC) and the walk unrolls completely.
 #define L1B_XLOOP(WIDTH) _Pragma("unroll") for (int it_ = 0, x = w.li * VEC; (NX > 0 ? it_ < NX : x < (WIDTH)); it_++, x += step)
 
+// Edge-outer walk for the widths whose vector count per lane is a compile-time constant (NX > 0): every
+// list entry (a slot of the destination or an incoming edge of the source) is decoded ONCE -- index,
+// weight, row address -- and its NX vectors are fetched at immediate offsets, instead of walking the whole
+// list once per vector (which repeated the decoding, and in the source lists an integer division, NX times).
+//   MODE 0: acc += weight * row      MODE 1: acc += sign(own - row) * weight      MODE 2: acc += sign(row - own) * weight
+// entry(i, ptr, weight) fills the row pointer of entry i (already at this lane's first vector; any valid
+// address when the entry is absent) and its weight, and returns whether the entry exists.
+constexpr int UE = 2; // entries in flight per lane: UE * NX 16-byte loads
+template <typename S, typename T, int VEC, int NX, int MODE, typename F>
+__device__ __forceinline__ void walk_list(Pack<T, VEC> (&acc)[NX], const Pack<T, VEC> (&own)[NX], int n, int step, F entry)
+{
+	for (int e0 = 0; e0 < n; e0 += UE) {
+		T wgt[UE];
+		const S *ptr[UE];
+		bool ok[UE];
+#pragma unroll
+		for (int u = 0; u < UE; u++) {
+			wgt[u] = T(0);
+			ok[u] = entry(e0 + u < n ? e0 + u : e0, ptr[u], wgt[u]) && e0 + u < n;
+			if (!ok[u])
+				wgt[u] = T(0);
+		}
+		Pack<T, VEC> row[UE][NX];
+#pragma unroll
+		for (int u = 0; u < UE; u++)
+#pragma unroll
+			for (int it = 0; it < NX; it++)
+				row[u][it] = ldc<S, T, VEC>(ptr[u] + it * step, ok[u]);
+#pragma unroll
+		for (int u = 0; u < UE; u++)
+#pragma unroll
+			for (int it = 0; it < NX; it++)
+#pragma unroll
+				for (int i = 0; i < VEC; i++) {
+					if (MODE == 0)
+						acc[it].v[i] += wgt[u] * row[u][it].v[i];
+					else if (MODE == 1)
+						acc[it].v[i] += sign_apply(own[it].v[i] - row[u][it].v[i], wgt[u]);
+					else
+						acc[it].v[i] += sign_apply(row[u][it].v[i] - own[it].v[i], wgt[u]);
+				}
+	}
+}
+template <typename T, int VEC, int NX> __device__ __forceinline__ void zero_acc(Pack<T, VEC> (&acc)[NX])
+{
+#pragma unroll
+	for (int it = 0; it < NX; it++)
+#pragma unroll
+		for (int i = 0; i < VEC; i++)
+			acc[it].v[i] = T(0);
+}
+
 // ---- forward, dst pass: scores -> exp -> (+1)-softmax -> attn, vo[dst] = sum_r a_r v[src_r] ----
 template <typename S, typename T, int VEC, int LPHC, int NX>
 __global__ void __launch_bounds__(256) sparse_fwd_dst_kernel(SparseArgs a, const S *__restrict__ v,
@@ -192,6 +244,25 @@ __global__ void __launch_bounds__(256) sparse_fwd_dst_kernel(SparseArgs a, const
 	__syncwarp();
 
 	S *orow = vo + ((tokrow + dst) * H + hh) * Wv;
+	if constexpr (NX > 0) {
+		Pack<T, VEC> acc[NX];
+		zero_acc(acc);
+		const S *vbase = v + (tokrow * H + hh) * Wv + w.li * VEC;
+		walk_list<S, T, VEC, NX, 0>(acc, acc, dm, step, [&](int r, const S *&ptr, T &wgt) {
+			const int src = slots[r];
+			const bool ok = w.head_ok && src >= 0;
+			ptr = vbase + size_t(ok ? src : 0) * H * Wv;
+			if (ok)
+				wgt = ld1<S, T>(arow + size_t(r) * H);
+			return ok;
+		});
+		if (w.head_ok) {
+#pragma unroll
+			for (int it = 0; it < NX; it++)
+				stc<S, T, VEC>(orow + w.li * VEC + it * step, acc[it]);
+		}
+		return;
+	}
 	L1B_XLOOP(Wv) {
 		Pack<T, VEC> acc = ldv<T, VEC>(nullptr, false);
 		for (int r0 = 0; r0 < dm; r0 += U) {
@@ -231,6 +302,27 @@ __global__ void __launch_bounds__(256) sparse_fwd_src_kernel(SparseArgs a, const
 	const int lph = LPHC > 0 ? LPHC : a.lph;
 	const int step = lph * VEC;
 	S *orow = vo + ((tokrow + src) * H + w.h) * Wv;
+	if constexpr (NX > 0) {
+		Pack<T, VEC> acc[NX];
+		zero_acc(acc);
+		const S *bbase = vb + (tokrow * H + w.h) * Wv + w.li * VEC;
+		const S *abase = attn + (tokrow * dm) * H + w.h;
+		walk_list<S, T, VEC, NX, 0>(acc, acc, e1 - e0, step, [&](int e, const S *&ptr, T &wgt) {
+			const int slot = a.csc_slot[e0 + e];
+			ptr = bbase + size_t(slot / dm) * H * Wv;
+			wgt = ld1<S, T>(abase + size_t(slot) * H);
+			return true;
+		});
+#pragma unroll
+		for (int it = 0; it < NX; it++) {
+			Pack<T, VEC> cur = ldc<S, T, VEC>(orow + w.li * VEC + it * step, true);
+#pragma unroll
+			for (int i = 0; i < VEC; i++)
+				cur.v[i] += acc[it].v[i];
+			stc<S, T, VEC>(orow + w.li * VEC + it * step, cur);
+		}
+		return;
+	}
 	L1B_XLOOP(Wv) {
 		Pack<T, VEC> acc = ldv<T, VEC>(nullptr, false);
 		for (int eb = e0; eb < e1; eb += U) {
@@ -342,6 +434,50 @@ __global__ void __launch_bounds__(256) sparse_bwd_dst_kernel(SparseArgs a, const
 
 	const T *qrow = q + ((tokrow + dst) * H + hh) * W;
 	T *orow = d_q + ((tokrow + dst) * H + hh) * W;
+	if constexpr (NX > 0) {
+		Pack<T, VEC> acc[NX], qv[NX];
+		zero_acc(acc);
+#pragma unroll
+		for (int it = 0; it < NX; it++)
+			qv[it] = ldv<T, VEC>(qrow + w.li * VEC + it * step, w.head_ok);
+		const T *kbase = k + (tokrow * H + hh) * W + w.li * VEC;
+		walk_list<T, T, VEC, NX, 1>(acc, qv, dm, step, [&](int r, const T *&ptr, T &wgt) {
+			const int src = slots[r];
+			const bool ok = w.head_ok && src >= 0;
+			ptr = kbase + size_t(ok ? src : 0) * H * W;
+			if (ok)
+				wgt = xrow[size_t(r) * H];
+			return ok;
+		});
+		if (w.head_ok) {
+#pragma unroll
+			for (int it = 0; it < NX; it++) {
+#pragma unroll
+				for (int i = 0; i < VEC; i++)
+					acc[it].v[i] *= scale;
+				*reinterpret_cast<Pack<T, VEC> *>(orow + w.li * VEC + it * step) = acc[it];
+			}
+		}
+		if (a.bidi) { // d_vb[dst] = sum_r a_r dvo[src_r]
+			T *brow = d_vb + ((tokrow + dst) * H + hh) * Wv;
+			zero_acc(acc);
+			const T *gbase = dvo + (tokrow * H + hh) * Wv + w.li * VEC;
+			walk_list<T, T, VEC, NX, 0>(acc, acc, dm, step, [&](int r, const T *&ptr, T &wgt) {
+				const int src = slots[r];
+				const bool ok = w.head_ok && src >= 0;
+				ptr = gbase + size_t(ok ? src : 0) * H * Wv;
+				if (ok)
+					wgt = arow[size_t(r) * H];
+				return ok;
+			});
+			if (w.head_ok) {
+#pragma unroll
+				for (int it = 0; it < NX; it++)
+					*reinterpret_cast<Pack<T, VEC> *>(brow + w.li * VEC + it * step) = acc[it];
+			}
+		}
+		return;
+	}
 	L1B_XLOOP(W) {
 		const Pack<T, VEC> qv = ldv<T, VEC>(qrow + x, w.head_ok);
 		Pack<T, VEC> acc = ldv<T, VEC>(nullptr, false);
@@ -413,6 +549,42 @@ __global__ void __launch_bounds__(256) sparse_bwd_src_kernel(SparseArgs a, const
 	const int lph = LPHC > 0 ? LPHC : a.lph;
 	const int step = lph * VEC;
 	T *vrow = d_v + ((tokrow + src) * H + w.h) * Wv;
+	if constexpr (NX > 0) {
+		Pack<T, VEC> acc[NX], kv[NX];
+		zero_acc(acc);
+		const T *gbase = dvo + (tokrow * H + w.h) * Wv + w.li * VEC;
+		const T *abase = attn + (tokrow * dm) * H + w.h, *xbase = dx + (tokrow * dm) * H + w.h;
+		walk_list<T, T, VEC, NX, 0>(acc, acc, e1 - e0, step, [&](int e, const T *&ptr, T &wgt) {
+			const int slot = a.csc_slot[e0 + e];
+			ptr = gbase + size_t(slot / dm) * H * Wv;
+			wgt = abase[size_t(slot) * H];
+			return true;
+		});
+#pragma unroll
+		for (int it = 0; it < NX; it++)
+			*reinterpret_cast<Pack<T, VEC> *>(vrow + w.li * VEC + it * step) = acc[it];
+		const T *krow = k + ((tokrow + src) * H + w.h) * W;
+		T *orow = d_k + ((tokrow + src) * H + w.h) * W;
+#pragma unroll
+		for (int it = 0; it < NX; it++)
+			kv[it] = ldv<T, VEC>(krow + w.li * VEC + it * step, true);
+		zero_acc(acc);
+		const T *qbase = q + (tokrow * H + w.h) * W + w.li * VEC;
+		walk_list<T, T, VEC, NX, 2>(acc, kv, e1 - e0, step, [&](int e, const T *&ptr, T &wgt) {
+			const int slot = a.csc_slot[e0 + e];
+			ptr = qbase + size_t(slot / dm) * H * W;
+			wgt = xbase[size_t(slot) * H];
+			return true;
+		});
+#pragma unroll
+		for (int it = 0; it < NX; it++) {
+#pragma unroll
+			for (int i = 0; i < VEC; i++)
+				acc[it].v[i] *= -scale;
+			*reinterpret_cast<Pack<T, VEC> *>(orow + w.li * VEC + it * step) = acc[it];
+		}
+		return;
+	}
 	L1B_XLOOP(Wv) {
 		Pack<T, VEC> acc = ldv<T, VEC>(nullptr, false);
 		for (int eb = e0; eb < e1; eb += U) {
