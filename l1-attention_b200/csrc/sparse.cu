@@ -140,7 +140,8 @@ constexpr int U = 4;
 // list once per vector (which repeated the decoding, and in the source lists an integer division, NX times).
 //   MODE 0: acc += weight * row      MODE 1: acc += sign(own - row) * weight      MODE 2: acc += sign(row - own) * weight
 // entry(i, ptr, weight) fills the row pointer of entry i (already at this lane's first vector; any valid
-// address when the entry is absent) and its weight, and returns whether the entry exists.
+// address when the entry is absent: the row is then loaded but not used, which is cheaper than a
+// predicated load plus zero fill) and its weight, and returns whether the entry exists.
 constexpr int UE = 2; // entries in flight per lane: UE * NX 16-byte loads
 template <typename S, typename T, int VEC, int NX, int MODE, typename F>
 __device__ __forceinline__ void walk_list(Pack<T, VEC> (&acc)[NX], const Pack<T, VEC> (&own)[NX], int n, int step, F entry)
@@ -161,9 +162,10 @@ __device__ __forceinline__ void walk_list(Pack<T, VEC> (&acc)[NX], const Pack<T,
 		for (int u = 0; u < UE; u++)
 #pragma unroll
 			for (int it = 0; it < NX; it++)
-				row[u][it] = ldc<S, T, VEC>(ptr[u] + it * step, ok[u]);
+				row[u][it] = ldc<S, T, VEC>(ptr[u] + it * step, true);
 #pragma unroll
 		for (int u = 0; u < UE; u++)
+			if (ok[u])
 #pragma unroll
 			for (int it = 0; it < NX; it++)
 #pragma unroll
@@ -214,12 +216,13 @@ __global__ void __launch_bounds__(256) sparse_fwd_dst_kernel(SparseArgs a, const
 			part[u] = T(0);
 		}
 		L1B_XLOOP(W) {
-			const Pack<T, VEC> qv = ldc<S, T, VEC>(qrow + x, w.head_ok);
+			// rows of absent slots / heads past the end are read from a valid address and their
+			// scores discarded below: cheaper than predicated loads with zero fill
+			const Pack<T, VEC> qv = ldc<S, T, VEC>(qrow + x, true);
 			Pack<T, VEC> kv[U];
 #pragma unroll
 			for (int u = 0; u < U; u++)
-				kv[u] = ldc<S, T, VEC>(k + ((tokrow + (src[u] < 0 ? 0 : src[u])) * H + hh) * W + x,
-						    w.head_ok && src[u] >= 0);
+				kv[u] = ldc<S, T, VEC>(k + ((tokrow + (src[u] < 0 ? 0 : src[u])) * H + hh) * W + x, true);
 #pragma unroll
 			for (int u = 0; u < U; u++)
 #pragma unroll
@@ -386,14 +389,14 @@ __global__ void __launch_bounds__(256) sparse_bwd_dst_kernel(SparseArgs a, const
 			part[u] = T(0);
 		}
 		L1B_XLOOP(Wv) {
-			const Pack<T, VEC> gv = ldv<T, VEC>(gdst + x, w.head_ok);
+			// absent slots / heads past the end read a valid address; their sums are discarded below
+			const Pack<T, VEC> gv = ldv<T, VEC>(gdst + x, true);
 			Pack<T, VEC> vv[U], gs[U];
 #pragma unroll
 			for (int u = 0; u < U; u++) {
-				const bool ok = w.head_ok && src[u] >= 0;
 				const size_t off = ((tokrow + (src[u] < 0 ? 0 : src[u])) * H + hh) * Wv + x;
-				vv[u] = ldv<T, VEC>(v + off, ok);
-				gs[u] = ldv<T, VEC>(dvo + off, ok && a.bidi);
+				vv[u] = ldv<T, VEC>(v + off, true);
+				gs[u] = ldv<T, VEC>(dvo + off, a.bidi != 0);
 			}
 #pragma unroll
 			for (int u = 0; u < U; u++)
@@ -401,7 +404,7 @@ __global__ void __launch_bounds__(256) sparse_bwd_dst_kernel(SparseArgs a, const
 				for (int i = 0; i < VEC; i++)
 					part[u] += vv[u].v[i] * gv.v[i];
 			if (a.bidi) {
-				const Pack<T, VEC> bv = ldv<T, VEC>(bdst + x, w.head_ok);
+				const Pack<T, VEC> bv = ldv<T, VEC>(bdst + x, true);
 #pragma unroll
 				for (int u = 0; u < U; u++)
 #pragma unroll
