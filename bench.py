@@ -600,13 +600,17 @@ def run_ours(args, wl):
             return float(hdq[0, 0, 0, 0])
     else:
         hq, hk, hv, hdvo = (torch.randn(shape).pin_memory() for _ in range(4))
+        hvo, hdv, hdq, hdk = (torch.empty(shape).pin_memory() for _ in range(4))
+        hattn = torch.empty(tuple(attn.shape)).pin_memory()
         coo_np = coo_h
         nqk, na, nc = hq.numel() * 4, attn.numel() * 4, coo_np.nbytes
         h2d, d2h = (3 * nqk + nc) + (4 * nqk + na + nc), (nqk + na) + 3 * nqk
 
         def e2e_step():
-            vo_h, attn_h = cabi.sparse_fwd_host(hv.numpy(), hq.numpy(), hk.numpy(), coo_np, dm, True)
-            r = cabi.sparse_bwd_host(hdvo.numpy(), hv.numpy(), hq.numpy(), hk.numpy(), coo_np, attn_h, dm, True)
+            _, attn_h = cabi.sparse_fwd_host(hv.numpy(), hq.numpy(), hk.numpy(), coo_np, dm, True,
+                                             out=(hvo.numpy(), hattn.numpy()))
+            r = cabi.sparse_bwd_host(hdvo.numpy(), hv.numpy(), hq.numpy(), hk.numpy(), coo_np, attn_h, dm, True,
+                                     out=(hdv.numpy(), None, hdq.numpy(), hdk.numpy()))
             return float(r[0][0, 0, 0, 0])
     e2e_step()
     sync_all()

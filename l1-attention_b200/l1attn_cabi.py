@@ -129,32 +129,39 @@ def dense_bwd_host(d_attn, q, k, out=None):
     return dq, dk
 
 
-def sparse_fwd_host(v, q, k, coo, dst_mxlen, use_softmax=True, vb=None):
-    """vb given -> bidirectional operator.  Returns (vo, attn)."""
+def sparse_fwd_host(v, q, k, coo, dst_mxlen, use_softmax=True, vb=None, out=None):
+    """vb given -> bidirectional operator.  Returns (vo, attn); out=(vo, attn) reuses caller arrays
+    (pinned ones make the copies back run at full PCIe rate)."""
     q = _np(q)
     k, v = _np(k, q.dtype), _np(v, q.dtype)
     vb = None if vb is None else _np(vb, q.dtype)
     coo = _np(coo, np.int32)
     bs, n, h, w = q.shape
     wv = v.shape[3]
-    vo = np.empty((bs, n, h, wv), dtype=q.dtype)
-    attn = np.empty((bs, n, int(dst_mxlen), h), dtype=q.dtype)
+    if out is None:
+        vo = np.empty((bs, n, h, wv), dtype=q.dtype)
+        attn = np.empty((bs, n, int(dst_mxlen), h), dtype=q.dtype)
+    else:
+        vo, attn = out
     _check(lib().l1attn_sparse_fwd_host(_ptr(v), _ptr(vb), _ptr(q), _ptr(k), _ptr(coo), _ptr(vo), _ptr(attn),
                                         bs, n, h, w, wv, coo.shape[0], int(dst_mxlen), int(bool(use_softmax)),
                                         int(vb is not None), _dt(q)), "l1attn_sparse_fwd_host")
     return vo, attn
 
 
-def sparse_bwd_host(dvo, v, q, k, coo, attn, dst_mxlen, use_softmax=True, vb=None):
-    """Returns (d_v, d_q, d_k) or, with vb, (d_vf, d_vb, d_q, d_k)."""
+def sparse_bwd_host(dvo, v, q, k, coo, attn, dst_mxlen, use_softmax=True, vb=None, out=None):
+    """Returns (d_v, d_q, d_k) or, with vb, (d_vf, d_vb, d_q, d_k); out=(d_v, d_vb or None, d_q, d_k) reuses caller arrays."""
     q = _np(q)
     k, v, dvo, attn = _np(k, q.dtype), _np(v, q.dtype), _np(dvo, q.dtype), _np(attn, q.dtype)
     vb = None if vb is None else _np(vb, q.dtype)
     coo = _np(coo, np.int32)
     bs, n, h, w = q.shape
     wv = v.shape[3]
-    dv, dq, dk = np.empty_like(v), np.empty_like(q), np.empty_like(q)
-    dvb = np.empty_like(v) if vb is not None else None
+    if out is None:
+        dv, dq, dk = np.empty_like(v), np.empty_like(q), np.empty_like(q)
+        dvb = np.empty_like(v) if vb is not None else None
+    else:
+        dv, dvb, dq, dk = out
     _check(lib().l1attn_sparse_bwd_host(_ptr(dvo), _ptr(v), _ptr(vb), _ptr(q), _ptr(k), _ptr(coo), _ptr(attn),
                                         _ptr(dv), _ptr(dvb), _ptr(dq), _ptr(dk), bs, n, h, w, wv, coo.shape[0],
                                         int(dst_mxlen), int(bool(use_softmax)), int(vb is not None), _dt(q)),
