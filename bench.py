@@ -653,7 +653,11 @@ def run_ours(args, wl):
             nqk, na, nc = bs * n * h * w * 4.0, attn.numel() * 4.0, coo.numel() * 4.0
             alg_bytes = (3 * nqk + nqk + na + nc) + (4 * nqk + na + 3 * nqk + nc)
             roof = {"bound": "hbm", "kernel": "sparse fwd+bwd (4 kernels)", "achieved": alg_bytes / ((fwd_ms + bwd_ms) * 1e-3) / 1e9,
-                    "peak": pk["hbm_gbs"], "unit": "GB/s", "traffic": None, "peak_source": pk["source"]}
+                    "peak": pk["hbm_gbs"], "unit": "GB/s", "peak_source": pk["source"],
+                    # ncu dram__bytes_read+write of the three kernels of a step at bs=2 (profiles/sparse_kernels.md:
+                    # 58.1 + 88.0 + 84.5 MB), scaled by batch: every batch item streams its own tensors
+                    "traffic": (230.7e6 * bs / 2.0) if (n, h, w, wl.get("fan")) == (4096, 8, 64, 31) else None,
+                    "note": "summed over the step's kernels; they are bound by L2 gather latency, not by HBM"}
             roof["frac"] = roof["achieved"] / roof["peak"]
             alu = None
         cpu = None
