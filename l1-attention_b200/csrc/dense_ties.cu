@@ -8,8 +8,8 @@
 //
 // Exact, in two steps.  One CTA handles NC width columns of one (batch, head):
 //   1. filter: every k value sets two bits (two hash functions) of its column's bitmap in shared
-//      memory; a q value whose two bits are both set is a candidate.  With 128 bits per token (up to
-//      2048 tokens) the false-candidate rate is ~1/4096 per value: about one candidate per CTA;
+//      memory; a q value whose two bits are both set is a candidate.  With 64 bits per token (up to
+//      4096 tokens) the false-candidate rate is ~1/1024 per value: about four candidates per CTA;
 //   2. proof: every candidate value is compared, bit pattern against bit pattern, with all k values
 //      of its column (held in registers by the threads that loaded them).  Matching k rows and
 //      the candidate's q row are the rows that tie.
@@ -217,11 +217,12 @@ int dense_ties_launch(const float *q, const float *k, unsigned char *flags, int 
 {
 	if (width % 4 != 0 || n_tok >= (1 << 24))
 		return 1;
-	// 128 bits per token while four columns fit in 128 KiB of shared memory (n_tok <= 2048), fewer
+	// 64 bits per token (32 KiB per CTA at 1024 tokens: seven CTAs per SM hide the load latency; 128 bits per
+	// token held three and took twice the time for 1/4 of the false candidates) up to 4096 tokens, fewer
 	// beyond: more false candidates to prove, and past ~16k tokens the list overflows into the
 	// conservative marking.  Four columns per CTA keep the global loads 16 bytes wide.
 	int log2bits = 15;
-	while (log2bits < 18 && (1 << log2bits) < 128 * n_tok)
+	while (log2bits < 18 && (1 << log2bits) < 64 * n_tok)
 		log2bits++;
 	const BwdFlagLayout fl = bwd_flag_layout(bs, n_tok, n_heads, width);
 	L1B_CUDA(cudaMemsetAsync(flags, 0, fl.bytes(), st));
