@@ -63,7 +63,16 @@ def test_argument_validation_needs_no_gpu():
     assert lib.l1attn_sparse_build_index(None, 3, 4, 2, p, None, None) == -1
     assert lib.l1attn_sparse_build_index(p, 1, 1 << 20, 1 << 12, p, None, None) == -2  # slot table > 2^31
     assert lib.l1attn_expand_coo(None, 4, p, p, 0, 10, None, None) == -1
+    # fused consumer: unknown mode, zero value width, NULL tensor, 16-bit dtypes (sparse forward only)
+    assert lib.l1attn_dense_softmax_v_fwd(p, p, p, p, None, 1, 1, 1, 1, 1, 3, 0, None) == -1
+    assert lib.l1attn_dense_softmax_v_fwd(p, p, p, p, None, 1, 1, 1, 1, 0, 0, 0, None) == -1
+    assert lib.l1attn_dense_softmax_v_fwd(p, p, None, p, None, 1, 1, 1, 1, 1, 0, 0, None) == -1
+    assert lib.l1attn_dense_softmax_v_fwd(p, p, p, p, None, 1, 1, 1, 1, 1, 0, 2, None) == -1
+    assert lib.l1attn_dense_softmax_v_bwd_dx(p, p, p, p, p, None, p, p, 1, 1, 1, 1, 1, 0, None) == -1
+    assert lib.l1attn_dense_fwd(p, p, p, 1, 1, 1, 1, 2, None) == -1  # float16 is not a dense dtype
+    assert lib.l1attn_sparse_bwd(p, p, None, p, p, p, p, p, None, p, p, p, 1, 1, 1, 1, 1, 1, 1, 1, 0, 2, None) == -1
     # empty problems are fine and touch nothing
+    assert lib.l1attn_dense_softmax_v_fwd(None, None, None, None, None, 0, 4, 2, 8, 8, 0, 0, None) == 0
     assert lib.l1attn_dense_fwd(None, None, None, 0, 5, 2, 8, 0, None) == 0
     assert lib.l1attn_dense_bwd(None, None, None, None, None, None, 3, 0, 2, 8, 1, None) == 0
 
