@@ -61,10 +61,12 @@ struct BwdItem {
 __device__ __forceinline__ BwdItem decode(const BwdWork &wk, unsigned r)
 {
 	BwdItem it;
-	it.x0 = int(r % wk.nxt) * TX;
-	r /= wk.nxt;
+	// width slices of one x tile are neighbours in the item order: the CTAs that work on them at the same
+	// time stream the same G tiles, so the second reader finds them in L2 (matters when width > 64)
 	it.w0 = int(r % wk.nws) * WS;
 	r /= wk.nws;
+	it.x0 = int(r % wk.nxt) * TX;
+	r /= wk.nxt;
 	it.h0 = int(r % wk.nhg) * HG;
 	it.b = int(r / wk.nhg);
 	return it;
