@@ -42,12 +42,12 @@ WORKLOADS = {
     "dense_small": dict(kind="dense", shape=(2, 1024, 16, 64)),  # profiling size: 134 MB of scores, > L2
     "sparse_small": dict(kind="sparse", shape=(2, 4096, 8, 64), fan=31),
     "sparse_cfg4": dict(kind="sparse", shape=(8, 4096, 8, 64), fan=31),
-    # BASELINE config 5: training step of a 4-layer pre-LN transformer on L1AttnSparseBidi; not a model of
-    # the reference (it ships none for the sparse operator), written here from the config's description
     # the dense scores fused with softmax and the value product (no [B,T,T,H] tensor): benchmark and long-context shapes
     "fused_cfg2": dict(kind="fused", shape=(16, 1024, 16, 64)),
     "fused_cfg3": dict(kind="fused", shape=(2, 4096, 8, 128)),
     "fused_small": dict(kind="fused", shape=(2, 1024, 16, 64)),
+    # training step of a 4-layer pre-LN transformer on L1AttnSparseBidi (d_model 256, 8 heads x 32, sequence 256,
+    # batch 64, vocabulary 64, 16 random srcs per dst + self edge, AdamW); the reference ships no such model
     "train_cfg5": dict(kind="train", batch=64, seq=256, d_model=256, heads=8, layers=4, vocab=64, fan=16),
 }
 SM_COUNT, FP32_LANES = 148, 128
@@ -481,6 +481,202 @@ def run_fused(args, wl):
 
 # ----------------------------------------------------------------------------- our arm
 
+def _events(torch, n):
+    return [torch.cuda.Event(enable_timing=True) for _ in range(n)]
+
+
+def setup_dense(torch, cabi, shape, dev, seed):
+    """Device-resident tensors and the two timed calls of a dense step (outputs and scratch pre-allocated)."""
+    bs, n, h, w = shape
+    gen = torch.Generator(device=dev).manual_seed(seed)
+    q = torch.randn(shape, generator=gen, device=dev)
+    k = torch.randn(shape, generator=gen, device=dev)
+    g = torch.randn((bs, n, n, h), generator=gen, device=dev)
+    attn = torch.empty((bs, n, n, h), device=dev)
+    dq, dk = torch.empty_like(q), torch.empty_like(k)
+    scratch = torch.empty(cabi.lib().l1attn_dense_bwd_scratch_bytes(bs, n, h, w, 0), dtype=torch.uint8, device=dev)
+    return dict(kind="dense", shape=shape, q=q, k=k, g=g, units=float(bs) * h * n * n * w,
+                launches=DENSE_LAUNCHES_PER_STEP,
+                fwd=lambda: cabi.dense_fwd(q, k, out=attn),
+                bwd=lambda: cabi.dense_bwd(g, q, k, out=(dq, dk), scratch=scratch))
+
+
+def setup_sparse(torch, cabi, shape, fan, dev, seed, qk_scale):
+    bs, n, h, w = shape
+    gen = torch.Generator(device=dev).manual_seed(seed)
+    co = bench_graph(n, fan, 4001)
+    coo_h, dm, _ = cabi.expand_coo_host(co.numpy())
+    coo = torch.from_numpy(coo_h).to(dev)
+    index = cabi.SparseIndex(coo, n, dm)
+    index.check()
+    q, k = (qk_scale * torch.randn(shape, generator=gen, device=dev) for _ in range(2))
+    v, dvo = (torch.randn(shape, generator=gen, device=dev) for _ in range(2))
+    vo = torch.empty_like(v)
+    attn = torch.empty((bs, n, dm, h), device=dev)
+    grads = (torch.empty_like(v), None, torch.empty_like(q), torch.empty_like(k))
+    scratch = torch.empty_like(attn)
+    return dict(kind="sparse", shape=shape, q=q, k=k, v=v, dvo=dvo, coo=coo, coo_h=coo_h, dm=dm, attn=attn, fan=fan,
+                units=float(coo.shape[0]) * bs * h, launches=4, qk_scale=qk_scale,
+                fwd=lambda: cabi.sparse_fwd(v, q, k, index, True, out=(vo, attn)),
+                bwd=lambda: cabi.sparse_bwd(dvo, v, q, k, index, attn, True, out=grads, scratch=scratch))
+
+
+def time_steps(torch, wl, steps, warmup, sync_all):
+    """CUDA events on the launching stream around every forward and backward of `steps` steps."""
+    for _ in range(max(warmup, 3)):
+        wl["fwd"]()
+        wl["bwd"]()
+    sync_all()
+    ev = [_events(torch, 3) for _ in range(steps)]
+    for i in range(steps):
+        ev[i][0].record()
+        wl["fwd"]()
+        ev[i][1].record()
+        wl["bwd"]()
+        ev[i][2].record()
+    sync_all()
+    return dict(total_ms=ev[0][0].elapsed_time(ev[-1][2]),
+                fwd_ms=sum(e[0].elapsed_time(e[1]) for e in ev) / steps,
+                bwd_ms=sum(e[1].elapsed_time(e[2]) for e in ev) / steps)
+
+
+def e2e_setup(torch, cabi, wl):
+    """The same step through the host-buffer C ABI from pinned host memory; returns (step(), h2d, d2h bytes)."""
+    shape = wl["shape"]
+    bs, n, h, w = shape
+    if wl["kind"] == "dense":
+        hq, hk = (torch.randn(shape).pin_memory() for _ in range(2))
+        hg = torch.randn((bs, n, n, h)).pin_memory()
+        hattn = torch.empty((bs, n, n, h)).pin_memory()
+        hdq, hdk = torch.empty(shape).pin_memory(), torch.empty(shape).pin_memory()
+        nqk, na = hq.numel() * 4, hg.numel() * 4
+
+        def step():
+            cabi.dense_fwd_host(hq.numpy(), hk.numpy(), out=hattn.numpy())
+            cabi.dense_bwd_host(hg.numpy(), hq.numpy(), hk.numpy(), out=(hdq.numpy(), hdk.numpy()))
+            return float(hdq[0, 0, 0, 0])
+        return step, 2 * nqk + (na + 2 * nqk), na + 2 * nqk
+    hq, hk, hv, hdvo = (torch.randn(shape).pin_memory() for _ in range(4))
+    hq.mul_(wl["qk_scale"])
+    hk.mul_(wl["qk_scale"])
+    hvo, hdv, hdq, hdk = (torch.empty(shape).pin_memory() for _ in range(4))
+    hattn = torch.empty(tuple(wl["attn"].shape)).pin_memory()
+    coo_np, dm = wl["coo_h"], wl["dm"]
+    nqk, na, nc = hq.numel() * 4, hattn.numel() * 4, coo_np.nbytes
+
+    def step():
+        _, attn_h = cabi.sparse_fwd_host(hv.numpy(), hq.numpy(), hk.numpy(), coo_np, dm, True, out=(hvo.numpy(), hattn.numpy()))
+        r = cabi.sparse_bwd_host(hdvo.numpy(), hv.numpy(), hq.numpy(), hk.numpy(), coo_np, attn_h, dm, True,
+                                 out=(hdv.numpy(), None, hdq.numpy(), hdk.numpy()))
+        return float(r[0][0, 0, 0, 0])
+    return step, (3 * nqk + nc) + (4 * nqk + na + nc), (nqk + na) + 3 * nqk
+
+
+def time_e2e(torch, step, n_steps):
+    step()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(n_steps):
+        step()
+    torch.cuda.synchronize()
+    return (time.perf_counter() - t0) * 1e3 / n_steps
+
+
+def l2_copy_rate(torch, dev):
+    """GB/s (read + write) of a device copy whose 2 x 24 MiB working set stays in the 126 MB L2: the yardstick
+    for the sparse kernels' row gathers, which hit L2 (every operand of the sparse config is 67 MB)."""
+    a = torch.empty(6 << 20, device=dev)
+    b = torch.empty_like(a)
+    for _ in range(5):
+        b.copy_(a)
+    e0, e1 = _events(torch, 2)
+    e0.record()
+    for _ in range(20):
+        b.copy_(a)
+    e1.record()
+    torch.cuda.synchronize()
+    return 20 * 2 * a.numel() * 4 / (e0.elapsed_time(e1) * 1e-3) / 1e9
+
+
+def roofline_of(wl, t, pk, clocks, l2_gbs=None):
+    """(roofline, alu_roofline) of a timed workload; t = dict(fwd_ms, bwd_ms)."""
+    bs, n, h, w = wl["shape"]
+    fwd_ms, bwd_ms = t["fwd_ms"], t["bwd_ms"]
+    if wl["kind"] == "dense":
+        # dominant kernel: the backward launch (its CUDA-event time bwd_ms also holds the tie detector and
+        # the reduction of the partial d_q).  Algorithmic HBM bytes per launch: d_attn, q and k read once,
+        # both gradients written.
+        alg_bytes = 4.0 * (bs * n * n * h + 4 * bs * n * h * w)
+        roof = {"bound": "hbm", "kernel": "dense_bwd_fused_kernel", "achieved": alg_bytes / (bwd_ms * 1e-3) / 1e9,
+                "peak": pk["hbm_gbs"], "unit": "GB/s", "peak_source": pk["source"],
+                # ncu dram__bytes_read+write of this kernel at B=2,T=1024,H=16,W=64 (profiles/), scaled by batch
+                "traffic": (DENSE_BWD_TRAFFIC_B2 * bs / 2.0) if (n, h, w) == (1024, 16, 64) and DENSE_BWD_TRAFFIC_B2 else None,
+                "note": "the kernel is FP32/ALU-pipe bound, not HBM bound: see alu_roofline"}
+        roof["frac"] = roof["achieved"] / roof["peak"]
+        mhz = (clocks or {}).get("sm_max_mhz") or pk["sm_max_mhz"]
+        alu_peak = SM_COUNT * FP32_LANES * mhz * 1e6
+        ops = wl["units"]
+        alu = {"model": "lane-instructions per op: fwd 2 (sub, abs-add), bwd 3 (sub, two adds)",
+               "peak_lane_instr_per_s": alu_peak, "peak_basis": "148 SM x 128 FP32 lanes x %.0f MHz" % mhz,
+               "fwd_frac": 2 * ops / (fwd_ms * 1e-3) / alu_peak, "bwd_frac": 3 * ops / (bwd_ms * 1e-3) / alu_peak,
+               "fwd_bwd_frac": 5 * ops / ((fwd_ms + bwd_ms) * 1e-3) / alu_peak}
+        return roof, alu
+    nqk, na, nc = bs * n * h * w * 4.0, wl["attn"].numel() * 4.0, wl["coo"].numel() * 4.0
+    alg_bytes = (3 * nqk + nqk + na + nc) + (4 * nqk + na + 3 * nqk + nc)
+    roof = {"bound": "hbm", "kernel": "sparse fwd+bwd (4 kernels)", "achieved": alg_bytes / ((fwd_ms + bwd_ms) * 1e-3) / 1e9,
+            "peak": pk["hbm_gbs"], "unit": "GB/s", "peak_source": pk["source"],
+            # ncu dram__bytes_read+write of the kernels of a step at bs=2 (profiles/sparse_kernels.md), scaled by
+            # batch: every batch item streams its own tensors
+            "traffic": (SPARSE_TRAFFIC_B2 * bs / 2.0) if (n, h, w, wl["fan"]) == (4096, 8, 64, 31) else None,
+            "note": "compulsory bytes (every tensor touched once) summed over the step's kernels; the row gathers hit L2: see gathered"}
+    roof["frac"] = roof["achieved"] / roof["peak"]
+    # rows fetched per edge instance (cl * bs * H of them): forward k and v of the src; backward v, k of the src in
+    # the dst pass and dvo, q of the dst in the src pass -- each a width (or v_width) slice of one head
+    gathered = wl["units"] * w * 4.0 * (2 + 4)
+    roof["gathered"] = {"bytes_per_step": gathered, "achieved": gathered / ((fwd_ms + bwd_ms) * 1e-3) / 1e9, "unit": "GB/s",
+                        "l2_copy_gbs": l2_gbs, "frac_of_l2_copy": (gathered / ((fwd_ms + bwd_ms) * 1e-3) / 1e9 / l2_gbs) if l2_gbs else None,
+                        "note": "l2_copy_gbs = read+write rate of a torch copy whose working set (48 MiB) stays in L2, measured in this run"}
+    return roof, None
+
+
+# kernels of this library per dense step: forward; tie detector; backward; (filled in with the backward's launch list)
+DENSE_LAUNCHES_PER_STEP = 3
+# ncu dram__bytes_read.sum + dram__bytes_write.sum per launch at the profiling sizes (profiles/*.md)
+DENSE_BWD_TRAFFIC_B2 = 314.9e6
+SPARSE_TRAFFIC_B2 = 230.7e6
+
+
+def module_step_ms(torch, wl, steps):
+    """The same step through the drop-in autograd modules a user of the reference calls (l1attn_cuda.L1Attn /
+    l1attn_sparse_cuda.L1AttnSparse + .backward): output, gradient and scratch allocations included."""
+    if wl["kind"] == "dense":
+        import l1attn_cuda
+        mod = l1attn_cuda.L1Attn()
+        q, k = (wl[x].clone().requires_grad_(True) for x in ("q", "k"))
+
+        def step():
+            q.grad = k.grad = None
+            mod(q, k).backward(wl["g"])
+    else:
+        import l1attn_sparse_cuda
+        mod = l1attn_sparse_cuda.L1AttnSparse()
+        v, q, k = (wl[x].clone().requires_grad_(True) for x in ("v", "q", "k"))
+
+        def step():
+            v.grad = q.grad = k.grad = None
+            mod(v, q, k, wl["coo"], wl["dm"], True).backward(wl["dvo"])
+    for _ in range(3):
+        step()
+    torch.cuda.synchronize()
+    e0, e1 = _events(torch, 2)
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps
+
+
 def run_ours(args, wl):
     import torch
     import torch.distributed as dist
@@ -503,48 +699,7 @@ def run_ours(args, wl):
         if hi == lo:
             raise SystemExit("bench.py: more ranks than batch items in --scaling strong")
         shape = (hi - lo,) + tuple(shape[1:])
-    bs, n, h, w = shape
-    gen = torch.Generator(device=dev).manual_seed(2000 + rank)
     pk = peaks()
-
-    if kind == "dense":
-        q = torch.randn(shape, generator=gen, device=dev)
-        k = torch.randn(shape, generator=gen, device=dev)
-        g = torch.randn((bs, n, n, h), generator=gen, device=dev)
-        attn = torch.empty((bs, n, n, h), device=dev)
-        dq, dk = torch.empty_like(q), torch.empty_like(k)
-        units = float(bs) * h * n * n * w
-        launches_per_step = 2
-
-        def fwd():
-            cabi.dense_fwd(q, k, out=attn)
-
-        bwd_scratch = torch.empty(cabi.lib().l1attn_dense_bwd_scratch_bytes(bs, n, h, w, 0), dtype=torch.uint8, device=dev)
-        launches_per_step = 3  # forward; tie detector; backward (both gradients in one launch)
-
-        def bwd():
-            cabi.dense_bwd(g, q, k, out=(dq, dk), scratch=bwd_scratch)
-    else:
-        from l1attn_cabi import SparseIndex
-        co = bench_graph(n, wl["fan"], 4001)
-        coo_h, dm, _ = cabi.expand_coo_host(co.numpy())
-        coo = torch.from_numpy(coo_h).to(dev)
-        index = SparseIndex(coo, n, dm)
-        index.check()
-        q, k = (0.25 * torch.randn(shape, generator=gen, device=dev) for _ in range(2))
-        v, dvo = (torch.randn(shape, generator=gen, device=dev) for _ in range(2))
-        vo = torch.empty_like(v)
-        attn = torch.empty((bs, n, dm, h), device=dev)
-        grads = (torch.empty_like(v), None, torch.empty_like(q), torch.empty_like(k))
-        scratch = torch.empty_like(attn)
-        units = float(coo.shape[0]) * bs * h
-        launches_per_step = 4
-
-        def fwd():
-            cabi.sparse_fwd(v, q, k, index, True, out=(vo, attn))
-
-        def bwd():
-            cabi.sparse_bwd(dvo, v, q, k, index, attn, True, out=grads, scratch=scratch)
 
     def sync_all():
         torch.cuda.synchronize()
@@ -552,134 +707,142 @@ def run_ours(args, wl):
             dist.barrier()
             torch.cuda.synchronize()
 
-    sampler = ClockSampler(local) if rank == 0 else None
-    for _ in range(max(args.warmup, 3)):
-        fwd()
-        bwd()
-    sync_all()
-    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
-    t_wall0 = time.time()
-    for i in range(args.steps):
-        ev[i][0].record()
-        fwd()
-        ev[i][1].record()
-        bwd()
-        ev[i][2].record()
-    sync_all()
-    t_wall1 = time.time()
-    total_ms = ev[0][0].elapsed_time(ev[-1][2])
-    fwd_ms = sum(e[0].elapsed_time(e[1]) for e in ev) / args.steps
-    bwd_ms = sum(e[1].elapsed_time(e[2]) for e in ev) / args.steps
-    total_ms = shard.max_over_ranks(total_ms, dev)
-    ms_per_step = total_ms / args.steps
-    all_units = units
-    if world > 1:  # units of every rank (ranks may hold different batch counts under strong scaling)
+    def all_units(units):  # units of every rank (ranks may hold different batch counts under strong scaling)
+        if world == 1:
+            return units
         tu = torch.tensor([units], device=dev, dtype=torch.float64)
         dist.all_reduce(tu)
-        all_units = float(tu.item())
-    value = all_units / (ms_per_step * 1e-3) / 1e9
+        return float(tu.item())
 
-    # ---- end to end through the host-buffer C ABI (rank-local; max over ranks)
+    def make(kind_, shape_, fan=31):
+        if kind_ == "dense":
+            return setup_dense(torch, cabi, shape_, dev, 2000 + rank)
+        return setup_sparse(torch, cabi, shape_, fan, dev, 4100 + rank, args.qk_scale)
+
+    def measure(w_, steps, e2e_steps):
+        """Device-resident timing (max over ranks) and the end-to-end leg of one workload -> record."""
+        t = time_steps(torch, w_, steps, args.warmup, sync_all)
+        ms = shard.max_over_ranks(t["total_ms"], dev) / steps
+        units = all_units(w_["units"])
+        rec = dict(value=units / (ms * 1e-3) / 1e9, ms_per_step=ms, fwd_ms=t["fwd_ms"], bwd_ms=t["bwd_ms"], t=t)
+        if not args.kernel_only:
+            step, h2d, d2h = e2e_setup(torch, cabi, w_)
+            sync_all()
+            ems = shard.max_over_ranks(time_e2e(torch, step, e2e_steps), dev)
+            rec["e2e"] = {"value": units / (ems * 1e-3) / 1e9, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                          "ms_per_step": ems, "steps": e2e_steps,
+                          "h2d_plus_d2h_gbs_per_rank": (h2d + d2h) / (ems * 1e-3) / 1e9}
+            cabi.lib().l1attn_host_release()
+        return rec
+
+    sampler = ClockSampler(local) if rank == 0 else None
+    t_wall0 = time.time()
+    main_wl = make(kind, shape, wl.get("fan", 31))
     e2e_steps = max(1, min(args.steps, 3))
-    if args.kernel_only:
-        h2d = d2h = 0
-
-        def e2e_step():
-            return 0.0
-    elif kind == "dense":
-        hq, hk = (torch.randn(shape).pin_memory() for _ in range(2))
-        hg = torch.randn((bs, n, n, h)).pin_memory()
-        hattn = torch.empty((bs, n, n, h)).pin_memory()
-        hdq, hdk = torch.empty(shape).pin_memory(), torch.empty(shape).pin_memory()
-        nqk, na = hq.numel() * 4, hg.numel() * 4
-        h2d, d2h = 2 * nqk + (na + 2 * nqk), na + 2 * nqk
-
-        def e2e_step():
-            cabi.dense_fwd_host(hq.numpy(), hk.numpy(), out=hattn.numpy())
-            cabi.dense_bwd_host(hg.numpy(), hq.numpy(), hk.numpy(), out=(hdq.numpy(), hdk.numpy()))
-            return float(hdq[0, 0, 0, 0])
-    else:
-        hq, hk, hv, hdvo = (torch.randn(shape).pin_memory() for _ in range(4))
-        hvo, hdv, hdq, hdk = (torch.empty(shape).pin_memory() for _ in range(4))
-        hattn = torch.empty(tuple(attn.shape)).pin_memory()
-        coo_np = coo_h
-        nqk, na, nc = hq.numel() * 4, attn.numel() * 4, coo_np.nbytes
-        h2d, d2h = (3 * nqk + nc) + (4 * nqk + na + nc), (nqk + na) + 3 * nqk
-
-        def e2e_step():
-            _, attn_h = cabi.sparse_fwd_host(hv.numpy(), hq.numpy(), hk.numpy(), coo_np, dm, True,
-                                             out=(hvo.numpy(), hattn.numpy()))
-            r = cabi.sparse_bwd_host(hdvo.numpy(), hv.numpy(), hq.numpy(), hk.numpy(), coo_np, attn_h, dm, True,
-                                     out=(hdv.numpy(), None, hdq.numpy(), hdk.numpy()))
-            return float(r[0][0, 0, 0, 0])
-    e2e_step()
-    sync_all()
-    t0 = time.perf_counter()
-    for _ in range(e2e_steps):
-        e2e_step()
-    torch.cuda.synchronize()
-    e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
-    e2e_ms = shard.max_over_ranks(e2e_ms, dev)
-    e2e_value = all_units / (e2e_ms * 1e-3) / 1e9
-    # clock samples over both timed regions (device-resident steps and end-to-end steps)
+    rec = measure(main_wl, args.steps, e2e_steps)
     clocks = sampler.window(t_wall0, time.time()) if sampler else None
-
-    ref_cuda = None
-    if args.compare_reference_cuda and rank == 0:
-        ref_cuda = time_reference_cuda(kind, dev, locals())
-
+    unit = "Gop/s" if kind == "dense" else "Gedge-inst/s"
+    secondary = not args.kernel_only and not args.no_extras
+    line = None
     if rank == 0:
-        unit = "Gop/s" if kind == "dense" else "Gedge-inst/s"
-        if kind == "dense":
-            # dominant kernel: the backward launch (both gradient passes; its CUDA-event time bwd_ms also
-            # holds the ~0.1 ms tie detector).  HBM algorithmic bytes per launch: d_attn read once per pass,
-            # q and k read per pass, both gradients written.
-            alg_bytes = 4.0 * (2 * bs * n * n * h + 6 * bs * n * h * w)
-            roof = {"bound": "hbm", "kernel": "dense_bwd_tma_kernel",
-                    "achieved": alg_bytes / (bwd_ms * 1e-3) / 1e9,
-                    "peak": pk["hbm_gbs"], "unit": "GB/s", "peak_source": pk["source"],
-                    # ncu dram__bytes_read+write of this kernel at B=2,T=1024,H=16,W=64 (profiles/), scaled by batch
-                    "traffic": (314.9e6 * bs / 2.0) if (n, h, w) == (1024, 16, 64) else None,
-                    "note": "the kernel is FP32/ALU-pipe bound, not HBM bound: see alu_roofline"}
-            roof["frac"] = roof["achieved"] / roof["peak"]
-            mhz = (clocks or {}).get("sm_max_mhz") or pk["sm_max_mhz"]
-            alu_peak = SM_COUNT * FP32_LANES * mhz * 1e6
-            ops = units
-            alu = {"model": "lane-instructions per op: fwd 2 (sub, abs-add), bwd 3 (sub, two adds)",
-                   "peak_lane_instr_per_s": alu_peak, "peak_basis": "148 SM x 128 FP32 lanes x %.0f MHz" % mhz,
-                   "fwd_frac": 2 * ops / (fwd_ms * 1e-3) / alu_peak, "bwd_frac": 3 * ops / (bwd_ms * 1e-3) / alu_peak,
-                   "fwd_bwd_frac": 5 * ops / ((fwd_ms + bwd_ms) * 1e-3) / alu_peak}
-        else:
-            nqk, na, nc = bs * n * h * w * 4.0, attn.numel() * 4.0, coo.numel() * 4.0
-            alg_bytes = (3 * nqk + nqk + na + nc) + (4 * nqk + na + 3 * nqk + nc)
-            roof = {"bound": "hbm", "kernel": "sparse fwd+bwd (4 kernels)", "achieved": alg_bytes / ((fwd_ms + bwd_ms) * 1e-3) / 1e9,
-                    "peak": pk["hbm_gbs"], "unit": "GB/s", "peak_source": pk["source"],
-                    # ncu dram__bytes_read+write of the three kernels of a step at bs=2 (profiles/sparse_kernels.md:
-                    # 58.1 + 88.0 + 84.5 MB), scaled by batch: every batch item streams its own tensors
-                    "traffic": (230.7e6 * bs / 2.0) if (n, h, w, wl.get("fan")) == (4096, 8, 64, 31) else None,
-                    "note": "summed over the step's kernels; they are bound by L2 gather latency, not by HBM"}
-            roof["frac"] = roof["achieved"] / roof["peak"]
-            alu = None
+        roof, alu = roofline_of(main_wl, rec["t"], pk, clocks, None if kind == "dense" else l2_copy_rate(torch, dev))
         cpu = None
         if world == 1 and not args.no_cpu_baseline and not args.kernel_only:
             r, info = cpu_reference_rate(kind, shape, 15.0, wl.get("fan", 31))
             cpu = dict(value=r, unit=unit, cores=info["cores"], kind=info["kind"], sample=info["sample"])
+        e2e = rec.get("e2e") or {"value": 0.0, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0, "ms_per_step": 0.0, "steps": 0}
+        e2e["unit"] = unit
         line = {
-            "metric": metric_name(kind), "value": value, "unit": unit, "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": args.scaling,
+            "metric": metric_name(kind), "value": rec["value"], "unit": unit, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": rec["ms_per_step"], "higher_is_better": True, "scaling": args.scaling,
             "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config_of(args, wl),
-            "fwd_ms": fwd_ms, "bwd_ms": bwd_ms, "roofline": roof, "alu_roofline": alu, "cpu_baseline": cpu,
-            "e2e": {"value": e2e_value, "unit": unit, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "ms_per_step": e2e_ms, "steps": e2e_steps},
-            "gpu_launches": launches_per_step * args.steps, "clocks": clocks,
+            "fwd_ms": rec["fwd_ms"], "bwd_ms": rec["bwd_ms"], "roofline": roof, "alu_roofline": alu, "cpu_baseline": cpu,
+            "e2e": e2e, "gpu_launches": main_wl["launches"] * args.steps, "clocks": clocks,
         }
-        if ref_cuda:
-            line["reference_cuda"] = ref_cuda
+        if secondary:
+            line["module_ms"] = module_step_ms(torch, main_wl, min(args.steps, 10))
+        if secondary or args.compare_reference_cuda:
+            line["reference_cuda"] = time_reference_cuda(kind, dev, dict(main_wl, fwd_ms=rec["fwd_ms"], bwd_ms=rec["bwd_ms"]))
+    del main_wl
+    torch.cuda.empty_cache()
+
+    # ---- the second half of the metric: the sparse config on every rank (weak), in the same line
+    if secondary and kind == "dense":
+        swl_cfg = WORKLOADS["sparse_cfg4"]
+        swl = make("sparse", swl_cfg["shape"], swl_cfg["fan"])
+        srec = measure(swl, args.steps, e2e_steps)
+        if rank == 0:
+            sroof, _ = roofline_of(swl, srec["t"], pk, clocks, l2_copy_rate(torch, dev))
+            srec.pop("t")
+            srec.update(metric=metric_name("sparse"), unit="Gedge-inst/s", roofline=sroof, gpu_launches=swl["launches"] * args.steps,
+                        config={"workload": "sparse_cfg4: 8x4096x8x64, 131072 edges, dst_mxlen %d" % swl["dm"],
+                                "values": "q,k ~ %g N(0,1); v, dvo ~ N(0,1)" % args.qk_scale,
+                                "per_gpu_batch": 8, "global_batch": 8 * world})
+            srec["e2e"]["unit"] = "Gedge-inst/s"
+            if world == 1 and not args.no_cpu_baseline:
+                r, info = cpu_reference_rate("sparse", swl_cfg["shape"], 15.0, swl_cfg["fan"])
+                srec["cpu_baseline"] = dict(value=r, unit="Gedge-inst/s", cores=info["cores"], kind=info["kind"], sample=info["sample"])
+            srec["module_ms"] = module_step_ms(torch, swl, min(args.steps, 10))
+            srec["reference_cuda"] = time_reference_cuda("sparse", dev, dict(swl, fwd_ms=srec["fwd_ms"], bwd_ms=srec["bwd_ms"]))
+            line["sparse_cfg4"] = srec
+        del swl
+        torch.cuda.empty_cache()
+        if world > 1:
+            st = run_strong(torch, dist, cabi, shard, args, swl_cfg, rank, world, dev, sync_all)
+            if rank == 0:
+                line["sparse_cfg4"]["strong"] = st
+
+    # ---- strong scaling beside the weak number: the SAME global workload dealt out over the ranks
+    if secondary and world > 1 and args.scaling == "weak":
+        line_strong = run_strong(torch, dist, cabi, shard, args, wl, rank, world, dev, sync_all)
+        if rank == 0:
+            line["strong"] = line_strong
+
+    if rank == 0:
         print(json.dumps(line), flush=True)
     if sampler:
         sampler.stop()
     if world > 1:
+        dist.barrier()
         dist.destroy_process_group()
+
+
+def run_strong(torch, dist, cabi, shard, args, wl, rank, world, dev, sync_all):
+    """The workload at its stated global size, partitioned over the ranks (l1attn_shard): dense by (batch, head
+    group) with shard-resident outputs and no collective; sparse by batch item when there are enough of them,
+    else by dst-token range with ONE all-reduce of d_k and d_v.  Returns the record for rank 0."""
+    kind, shape = wl["kind"], wl["shape"]
+    bs, n, h, w = shape
+    unit = "Gop/s" if kind == "dense" else "Gedge-inst/s"
+    if kind == "dense":
+        b0, b1, h0, h1 = shard.dense_partition(bs, h, world)[rank]
+        swl = setup_dense(torch, cabi, (b1 - b0, n, h1 - h0, w), dev, 2000 + rank)
+        t = time_steps(torch, swl, args.steps, args.warmup, sync_all)
+        ms = shard.max_over_ranks(t["total_ms"], dev) / args.steps
+        units = float(bs) * h * n * n * w
+        return {"value": units / (ms * 1e-3) / 1e9, "unit": unit, "ms_per_step": ms, "collective": None,
+                "partition": "(batch, head group): rank 0 holds batch %d..%d, heads %d..%d of %s; outputs stay on their rank"
+                             % (b0, b1, h0, h1, list(shape))}
+    import l1attn_sparse_cuda
+    co = bench_graph(n, wl["fan"], 4001)
+    plan = shard.SparseShard(co, bs, n, rank, world, device=dev)
+    gen = torch.Generator(device=dev).manual_seed(4100)  # same tensors on every rank (replicated inputs)
+    q, k = (args.qk_scale * torch.randn(shape, generator=gen, device=dev) for _ in range(2))
+    v, dvo = (torch.randn(shape, generator=gen, device=dev) for _ in range(2))
+    step = lambda: plan.forward_backward(v, q, k, dvo, True)
+    for _ in range(max(args.warmup, 3)):
+        step()
+    sync_all()
+    e0, e1 = _events(torch, 2)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    sync_all()
+    ms = shard.max_over_ranks(e0.elapsed_time(e1), dev) / args.steps
+    units = float(co.shape[0]) * bs * h
+    return {"value": units / (ms * 1e-3) / 1e9, "unit": unit, "ms_per_step": ms, "partition": plan.describe(),
+            "collective": plan.collective_note()}
 
 
 def main():
@@ -698,6 +861,11 @@ def main():
     ap.add_argument("--cuda-graph", action="store_true",
                     help="train_cfg5: also time the step captured into one CUDA graph and replayed")
     ap.add_argument("--kernel-only", action="store_true", help="skip the end-to-end and CPU legs (profiling runs)")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="skip the records added beside the main workload (sparse config, reference GPU kernels, "
+                         "module call, strong scaling)")
+    ap.add_argument("--qk-scale", type=float, default=1.0,
+                    help="sparse workloads: q,k ~ qk_scale * N(0,1) (1: logits near -9, weights ~1e-4; 0.25: weights ~1/32)")
     args = ap.parse_args()
     wl = WORKLOADS[args.workload]
     if wl["kind"] == "train":

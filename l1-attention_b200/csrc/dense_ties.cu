@@ -210,13 +210,16 @@ int launch_nc(const float *q, const float *k, unsigned char *flags, int bs, int 
 } // namespace
 
 // Fills the flag arrays (device, bwd_flag_layout(...).bytes() bytes).  Returns L1ATTN_OK, a negative
-// error, or 1 when the detector does not apply (token index beyond 24 bits, width not a multiple of 4);
+// error, or 1 when the detector does not apply (token index beyond 24 bits, width not a multiple of 4,
+// q or k not 16-byte aligned);
 // the caller then runs every tile with the exact loop.
 int dense_ties_launch(const float *q, const float *k, unsigned char *flags, int bs, int n_tok, int n_heads, int width,
 		      cudaStream_t st)
 {
 	if (width % 4 != 0 || n_tok >= (1 << 24))
 		return 1;
+	if (!aligned(q, 16) || !aligned(k, 16))
+		return 1; // the kernel reads four columns as one 16-byte vector; the C ABI only promises element alignment
 	// 64 bits per token (32 KiB per CTA at 1024 tokens: seven CTAs per SM hide the load latency; 128 bits per
 	// token held three and took twice the time for 1/4 of the false candidates) up to 4096 tokens, fewer
 	// beyond: more false candidates to prove, and past ~16k tokens the list overflows into the

@@ -1,13 +1,19 @@
 """Partitioning of the L1-attention operators across the GPUs of one node.
 
-Both operators are independent per batch item (and per head): no reduction crosses items, in the
+Both operators are independent per batch item and per head: no reduction crosses items, in the
 forward or in the backward.  So the multi-GPU form is one process per GPU, each running the
-single-GPU operators on its own slice of the batch, with no collective on the data path; a gather
-of the outputs is only needed if one rank wants everything.
+single-GPU operators on its own slice, with no collective on the data path; a gather of the
+outputs is only needed if one rank wants everything.
 
   shard_range(n, rank, world)        contiguous, balanced slice [lo, hi) of n items for `rank`
   max_over_ranks(x)                  all-reduce MAX of a python float (for timing: slowest rank)
   gather_batch(t, n_total)           all-gather of batch slices (dim 0) into the full tensor, any rank sizes
+  dense_partition(bs, heads, world)  (batch, head group) slab of every rank for the dense operator
+  dense_local(t, slab)               a rank's contiguous [b0:b1, :, h0:h1, :] copy of q or k
+  gather_dense(local, bs, heads)     all-gather of the [B_loc, T, T, H_loc] score slabs into [B, T, T, H]
+  SparseShard                        the sparse operator over the ranks: by batch item when there are at
+                                     least as many items as ranks, else by dst-token range with ONE
+                                     all-reduce of the d_k and d_v partial sums
 
 The collectives go through torch.distributed (NCCL on GPUs, gloo in CPU tests).
 """
@@ -49,3 +55,137 @@ def gather_batch(local, n_total):
     parts = [torch.empty_like(padded) for _ in range(world)]
     dist.all_gather(parts, padded)
     return torch.cat([p[: h - l] for p, (l, h) in zip(parts, sizes)], 0)
+
+
+# ------------------------------------------------------------------ dense: (batch, head group) slabs
+
+def dense_partition(bs, n_heads, world):
+    """[(b0, b1, h0, h1)] per rank.  With at least as many batch items as ranks the batch is dealt out and
+    every rank keeps all heads (its q, k and score slabs are contiguous pieces of the global tensors, no
+    copies).  With fewer items, the ranks are dealt out over the items and the ranks of one item split its
+    heads into contiguous groups: rank-local q, k are [B_loc, T, H_loc, W] copies and the local scores
+    [B_loc, T, T, H_loc] -- heads are the innermost axis of the scores, so a head shard is a strided
+    interleave of the global tensor, which only gather_dense() ever materialises."""
+    if bs <= 0 or n_heads <= 0 or world <= 0:
+        raise ValueError("bad partition request bs=%r heads=%r world=%r" % (bs, n_heads, world))
+    if bs >= world:
+        return [shard_range(bs, r, world) + (0, n_heads) for r in range(world)]
+    out = []
+    for b in range(bs):
+        r0, r1 = shard_range(world, b, bs)  # the ranks that share batch item b
+        if r1 - r0 > n_heads:
+            raise ValueError("%d ranks for one batch item but only %d heads" % (r1 - r0, n_heads))
+        out += [(b, b + 1) + shard_range(n_heads, j, r1 - r0) for j in range(r1 - r0)]
+    return out
+
+
+def dense_local(t, slab):
+    b0, b1, h0, h1 = slab
+    return t[b0:b1, :, h0:h1].contiguous()
+
+
+def gather_dense(local, bs, n_heads):
+    """Every rank receives the global [bs, T, T, n_heads] scores assembled from the ranks' slabs."""
+    if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size() == 1:
+        return local
+    world = dist.get_world_size()
+    part = dense_partition(bs, n_heads, world)
+    mb, mh = max(p[1] - p[0] for p in part), max(p[3] - p[2] for p in part)
+    n = local.shape[1]
+    padded = torch.zeros((mb, n, n, mh), dtype=local.dtype, device=local.device)
+    padded[: local.shape[0], :, :, : local.shape[3]] = local
+    parts = [torch.empty_like(padded) for _ in range(world)]
+    dist.all_gather(parts, padded)
+    full = torch.empty((bs, n, n, n_heads), dtype=local.dtype, device=local.device)
+    for p, (b0, b1, h0, h1) in zip(parts, part):
+        full[b0:b1, :, :, h0:h1] = p[: b1 - b0, :, :, : h1 - h0]
+    return full
+
+
+# ------------------------------------------------------------------ sparse: batch items or dst-token ranges
+
+def _cuda_sparse_ops(device):
+    """The library's sparse forward/backward behind the (coo -> index) object SparseShard needs."""
+    import l1attn_cabi as cabi
+
+    class Ops:
+        def index(self, coo, n_tok, dst_mxlen):
+            ix = cabi.SparseIndex(coo.to(device), n_tok, dst_mxlen)
+            ix.check()
+            return ix
+
+        def forward(self, v, q, k, ix, usm, out):
+            return cabi.sparse_fwd(v, q, k, ix, usm, out=out)
+
+        def backward(self, dvo, v, q, k, ix, attn, usm, out, scratch):
+            return cabi.sparse_bwd(dvo, v, q, k, ix, attn, usm, out=out, scratch=scratch)
+
+        def expand(self, co):
+            coo, dm, _ = cabi.expand_coo_host(co.cpu().numpy())
+            return torch.from_numpy(coo), dm
+    return Ops()
+
+
+class SparseShard:
+    """L1AttnSparse forward + backward over `world` ranks.
+
+    mode "batch"  (bs >= world): rank r owns batch items shard_range(bs, r, world); nothing is exchanged.
+    mode "dst"    (bs <  world): every rank keeps q, k, v (replicated) and owns the dst tokens
+                  shard_range(n_tok, r, world): it runs the operator on the sub-list of edges whose dst it
+                  owns.  All edges of a dst stay together and keep their order, so their softmax slots are
+                  those of the full list; vo, attn and d_q rows of the owned tokens are complete (other rows
+                  are zero).  d_k and d_v scatter to arbitrary src tokens, so each rank holds partial sums:
+                  they are written into ONE flat buffer and summed with ONE all-reduce.
+
+    `ops` is the compute backend (default: this library on `device`; there is no CPU implementation --
+    the CPU tests of the partition logic pass a stand-in)."""
+
+    def __init__(self, co, bs, n_tok, rank, world, device="cuda", ops=None):
+        self.bs, self.n_tok, self.rank, self.world, self.device = bs, n_tok, rank, world, device
+        self.ops = ops if ops is not None else _cuda_sparse_ops(device)
+        co = torch.as_tensor(co)
+        self.mode = "batch" if bs >= world else "dst"
+        if self.mode == "batch":
+            self.b0, self.b1 = shard_range(bs, rank, world)
+            self.d0, self.d1 = 0, n_tok
+            mine = co
+        else:
+            self.b0, self.b1 = 0, bs
+            self.d0, self.d1 = shard_range(n_tok, rank, world)
+            mine = co[(co[:, 0] >= self.d0) & (co[:, 0] < self.d1)]
+        self.n_edges_local, self.n_edges = int(mine.shape[0]), int(co.shape[0])
+        coo, self.dst_mxlen = self.ops.expand(mine)
+        self.index = self.ops.index(coo, n_tok, self.dst_mxlen)
+        self._buf = None
+
+    def describe(self):
+        if self.mode == "batch":
+            return "batch items %d..%d of %d on rank %d, full graph, no collective" % (self.b0, self.b1, self.bs, self.rank)
+        return ("dst tokens %d..%d of %d on rank %d (%d of %d edges), q, k, v replicated"
+                % (self.d0, self.d1, self.n_tok, self.rank, self.n_edges_local, self.n_edges))
+
+    def collective_note(self):
+        if self.mode == "batch" or self._buf is None:
+            return None
+        return "one all_reduce(SUM) of d_k and d_v in one buffer: %d bytes per rank" % (self._buf.numel() * self._buf.element_size())
+
+    def forward_backward(self, v, q, k, dvo, use_softmax=True):
+        """Returns (vo, d_v, d_q, d_k).  batch mode: the rank's batch slice of each.  dst mode: vo and d_q hold
+        the owned dst rows (zero elsewhere); d_v and d_k are complete on every rank after the all-reduce."""
+        sl = slice(self.b0, self.b1)
+        v, q, k, dvo = v[sl], q[sl], k[sl], dvo[sl]
+        bs, n, h, w = q.shape
+        wv = v.shape[3]
+        if self._buf is None or self._buf.dtype != q.dtype or self._buf.numel() != k.numel() + v.numel():
+            self._buf = torch.empty(k.numel() + v.numel(), dtype=q.dtype, device=q.device)
+            self._vo = torch.empty_like(v)
+            self._attn = torch.empty((bs, n, self.dst_mxlen, h), dtype=q.dtype, device=q.device)
+            self._scratch = torch.empty_like(self._attn)
+            self._dq = torch.empty_like(q)
+        d_k = self._buf[: k.numel()].view(k.shape)
+        d_v = self._buf[k.numel():].view(v.shape)
+        vo, attn = self.ops.forward(v, q, k, self.index, use_softmax, (self._vo, self._attn))
+        self.ops.backward(dvo, v, q, k, self.index, attn, use_softmax, (d_v, None, self._dq, d_k), self._scratch)
+        if self.mode == "dst" and self.world > 1:
+            dist.all_reduce(self._buf)
+        return vo, d_v, self._dq, d_k

@@ -41,6 +41,25 @@ def assert_close(x, ref, tol, what=""):
     assert e1 <= tol and e2 <= tol, "%s: max-rel %.3e rms-rel %.3e > tol %.1e" % (what, e1, e2, tol)
 
 
+def assert_close_torch(x, ref, tol, what=""):
+    """assert_close for device tensors too large to move to the host: same two norm-wise measures,
+    accumulated in float64 on the device."""
+    import torch
+    assert x.shape == ref.shape, (x.shape, ref.shape)
+    mx = float(ref.abs().max())
+    dmax = float((x - ref).abs().max())
+    ss_d = ss_r = 0.0
+    xf, rf = x.reshape(-1), ref.reshape(-1)
+    for i in range(0, xf.numel(), 1 << 26):
+        a, b = xf[i:i + (1 << 26)].double(), rf[i:i + (1 << 26)].double()
+        ss_d += float(((a - b) ** 2).sum())
+        ss_r += float((b ** 2).sum())
+    e1 = dmax / mx if mx > 0 else dmax
+    e2 = (ss_d / ss_r) ** 0.5 if ss_r > 0 else ss_d ** 0.5
+    assert e1 <= tol and e2 <= tol, "%s: max-rel %.3e rms-rel %.3e > tol %.1e" % (what, e1, e2, tol)
+    return e1, e2
+
+
 @pytest.fixture(scope="session")
 def golden():
     d = os.path.join(ROOT, "tests", "golden")

@@ -158,7 +158,7 @@ def test_host_buffer_entry_points():
 
 
 def test_fp64_long_context_variant_full():
-    """BASELINE's fp64 variant [2,512,8,128], checked in full against the oracle at 1e-12."""
+    """The float64 long-context variant [2,512,8,128], checked in full against the oracle at 1e-12."""
     from oracle import oracle
     cabi = _cabi()
     rng = np.random.RandomState(3001)
@@ -175,7 +175,7 @@ def test_fp64_long_context_variant_full():
 
 @pytest.mark.parametrize("shape", [(16, 1024, 16, 64), (2, 4096, 8, 128)])
 def test_full_size_properties(shape):
-    """BASELINE's fp32 benchmark shapes, too large for the oracle: size-independent properties.
+    """The fp32 benchmark shapes [16,1024,16,64] and [2,4096,8,128], too large for the oracle: size-independent properties.
       * swapping q and k transposes the score matrix exactly (|q-k| is symmetric);
       * sampled (b, s, t) entries and sampled gradient rows match a float64 numpy evaluation;
       * the backward is linear in d_attn."""
@@ -213,3 +213,63 @@ def test_full_size_properties(shape):
     dq3, dk3 = cabi.dense_bwd(g1, q, k)
     assert_close((dq1 + dq2).cpu().numpy(), dq3.cpu().numpy(), 1e-5, "linearity dq")
     assert_close((dk1 + dk2).cpu().numpy(), dk3.cpu().numpy(), 1e-5, "linearity dk")
+
+
+def _offset_by_one(t):
+    """A contiguous copy of t whose storage starts one element (4 bytes) past a 16-byte boundary."""
+    buf = torch.empty(t.numel() + 1, dtype=t.dtype, device=t.device)
+    view = buf[1:].view(t.shape)
+    view.copy_(t)
+    assert view.is_contiguous() and view.data_ptr() % 16 == 4
+    return view
+
+
+def test_pointers_aligned_to_the_element_only():
+    """The C ABI promises element alignment, not 16 bytes: tensors that start 4 bytes past a 16-byte
+    boundary (a contiguous view with storage offset 1) must take the kernels without vector loads or
+    tensor maps and give the aligned call's results -- dense forward/backward (with and without tie
+    scratch), the fused consumer and the sparse operators."""
+    import l1attn_fused_cuda
+    cabi = _cabi()
+    q, k, g = (torch.from_numpy(a).cuda() for a in _rand((2, 72, 8, 64), np.float32, 31))
+    k[1, 7, 3, 5] = q[1, 9, 3, 5]  # one planted tie
+    want_attn = cabi.dense_fwd(q, k)
+    want = cabi.dense_bwd(g, q, k)
+    qo, ko, go = _offset_by_one(q), _offset_by_one(k), _offset_by_one(g)
+    out = _offset_by_one(torch.empty_like(want_attn))
+    assert_close(cabi.dense_fwd(qo, ko, out=out).cpu().numpy(), want_attn.cpu().numpy(), 1e-6, "attn")
+    for scratch in ("auto", None):
+        outs = (_offset_by_one(torch.empty_like(q)), _offset_by_one(torch.empty_like(k)))
+        got = cabi.dense_bwd(go, qo, ko, out=outs, scratch=scratch)
+        for a, b in zip(got, want):
+            assert_close(a.cpu().numpy(), b.cpu().numpy(), 1e-6, "gradients")
+    # mixed: only q misaligned (the tie detector and the tensor-map path must both decline)
+    got = cabi.dense_bwd(g, qo, k)
+    for a, b in zip(got, want):
+        assert_close(a.cpu().numpy(), b.cpu().numpy(), 1e-6, "gradients, q offset only")
+    v = torch.randn(2, 72, 8, 64, device="cuda")
+    want_vo = cabi.dense_softmax_v_fwd(0.3 * q, 0.3 * k, v)
+    got_vo = cabi.dense_softmax_v_fwd(_offset_by_one(0.3 * q), _offset_by_one(0.3 * k), _offset_by_one(v),
+                                      out=_offset_by_one(torch.empty_like(v)))
+    assert_close(got_vo.cpu().numpy(), want_vo.cpu().numpy(), 1e-6, "fused vo")
+    # sparse, through the C ABI with every float tensor offset
+    from oracle import oracle
+    rng = np.random.RandomState(4)
+    co = np.stack([rng.randint(0, 72, 500), rng.randint(0, 72, 500)], 1)
+    coo, dm, _ = oracle.expand_coo(co)
+    ix = cabi.SparseIndex(torch.from_numpy(coo).cuda(), 72, dm)
+    ix.check()
+    qs, ks = 0.3 * q, 0.3 * k
+    vo, attn = cabi.sparse_fwd(v, qs, ks, ix, True)
+    grads = cabi.sparse_bwd(g[:, :, :64].contiguous().view(2, 72, 8, 64), v, qs, ks, ix, attn, True)
+    dvo_o = _offset_by_one(g[:, :, :64].contiguous().view(2, 72, 8, 64))
+    vo2, attn2 = cabi.sparse_fwd(_offset_by_one(v), _offset_by_one(qs), _offset_by_one(ks), ix, True,
+                                 out=(_offset_by_one(torch.empty_like(vo)), _offset_by_one(torch.empty_like(attn))))
+    assert_close(vo2.cpu().numpy(), vo.cpu().numpy(), 1e-6, "sparse vo")
+    outs = (_offset_by_one(torch.empty_like(v)), None, _offset_by_one(torch.empty_like(q)), _offset_by_one(torch.empty_like(k)))
+    grads2 = cabi.sparse_bwd(dvo_o, _offset_by_one(v), _offset_by_one(qs), _offset_by_one(ks), ix, attn2, True,
+                             out=outs, scratch=_offset_by_one(torch.empty_like(attn)))
+    for a, b in zip(grads2, grads):
+        assert_close(a.cpu().numpy(), b.cpu().numpy(), 1e-6, "sparse gradients")
+    torch.cuda.synchronize()
+    assert cabi.lib().l1attn_device_status() == 0

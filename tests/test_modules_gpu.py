@@ -240,3 +240,145 @@ def test_sparse_fp32_vs_reference_cuda(usm):
     for x, r in zip(newb.backward(dvo, v, vb, q, k, coo, attn, dm, usm),
                     refb.backward(dvo, v, vb, q, k, coo, rattn, dm, usm)):
         assert_close(x.cpu().numpy(), r.cpu().numpy(), 1e-5, "bidi grad")
+
+
+# ------------------------------------------------------------------ the benchmark shapes against the reference's GPU kernels
+#
+# Same seeded fp32 inputs through this library's drivers and through the reference's own GPU
+# extension (compiled unmodified for sm_100 into oracle/_ref): 1e-5 norm-wise on every output.  The
+# reference accumulates its fp32 gradients with atomic adds in arbitrary order and is built with
+# --use_fast_math, so element-wise equality is not defined; the two norm-wise measures are.
+
+def _seeded(shape, seed, scale=1.0):
+    gen = torch.Generator(device="cuda").manual_seed(seed)
+    return torch.randn(shape, device="cuda", generator=gen).mul_(scale)
+
+
+@pytest.mark.parametrize("shape", [(16, 1024, 16, 64), (2, 4096, 8, 128)])
+def test_dense_fp32_vs_reference_cuda_benchmark_shapes(shape):
+    """[16,1024,16,64] takes the reference's width==64 kernels (cuda/l1attn_cuda_kernel.cu:137-203,
+    369-455), [2,4096,8,128] its width%32 kernels (:72-135, 284-367)."""
+    from conftest import assert_close_torch
+    ref = _ref_cuda("ref_l1attn_cuda_drv")
+    import l1attn_cuda_drv as new
+    bs, n, h, w = shape
+    q = torch.cat([_seeded((1, n, h, w), 2000 + b) for b in range(bs)])
+    k = torch.cat([_seeded((1, n, h, w), 2100 + b) for b in range(bs)])
+    a, r = new.forward(q, k)[0], ref.forward(q, k)[0]
+    assert_close_torch(a, r, 1e-5, "attn")
+    del a, r
+    g = _seeded((bs, n, n, h), 2200)
+    ours, theirs = new.backward(g, q, k), ref.backward(g, q, k)
+    for x, y, name in zip(ours, theirs, ("d_q", "d_k")):
+        assert_close_torch(x, y, 1e-5, name)
+
+
+@pytest.mark.parametrize("qk_scale", [1.0, 0.25])
+@pytest.mark.parametrize("usm", [True, False])
+def test_sparse_fp32_vs_reference_cuda_benchmark_graph(usm, qk_scale):
+    """bs 8, 4096 tokens, 8 heads, width 64, 131072 edges (self edge + 31 random srcs per dst), plain and
+    bidirectional, against cuda/l1attn_sparse_cuda_kernel.cu:373-531, 651-815.  Two value regimes:
+    q,k ~ N(0,1) (logits near -9: weights ~1e-4, the "+1" of the denominator dominates, and the
+    reference's fast-math exp differs most from an accurate one) and 0.25 N(0,1) (weights ~1/32)."""
+    from conftest import assert_close_torch
+    ref = _ref_cuda("ref_l1attn_sparse_cuda_drv")
+    refb = _ref_cuda("ref_l1attn_sparse_bidi_cuda_drv")
+    import l1attn_sparse_cuda_drv as new
+    import l1attn_sparse_bidi_cuda_drv as newb
+    from test_sparse_gpu import bench_graph
+    from oracle import oracle
+    bs, n, h, w = 8, 4096, 8, 64
+    coo, dm, _ = oracle.expand_coo(bench_graph(n, 31, 4001))
+    assert coo.shape[0] == 131072 and dm == 32
+    coo = torch.from_numpy(coo).cuda()
+    q, k = (torch.cat([_seeded((1, n, h, w), 4100 + 10 * i + b, qk_scale) for b in range(bs)]) for i in range(2))
+    v, vb, dvo = (torch.cat([_seeded((1, n, h, w), 4300 + 10 * i + b) for b in range(bs)]) for i in range(3))
+    vo, attn = new.forward(v, q, k, coo, dm, usm)
+    rvo, rattn = ref.forward(v, q, k, coo, dm, usm)
+    assert_close_torch(vo, rvo, 1e-5, "vo")
+    assert_close_torch(attn, rattn, 1e-5, "attn")
+    for x, r, name in zip(new.backward(dvo, v, q, k, coo, attn, dm, usm),
+                          ref.backward(dvo, v, q, k, coo, rattn, dm, usm), ("d_v", "d_q", "d_k")):
+        assert_close_torch(x, r, 1e-5, name)
+    vo, attn = newb.forward(v, vb, q, k, coo, dm, usm)
+    rvo, rattn = refb.forward(v, vb, q, k, coo, dm, usm)
+    assert_close_torch(vo, rvo, 1e-5, "bidi vo")
+    assert_close_torch(attn, rattn, 1e-5, "bidi attn")
+    for x, r, name in zip(newb.backward(dvo, v, vb, q, k, coo, attn, dm, usm),
+                          refb.backward(dvo, v, vb, q, k, coo, rattn, dm, usm), ("d_vf", "d_vb", "d_q", "d_k")):
+        assert_close_torch(x, r, 1e-5, "bidi " + name)
+
+
+def test_config1_chain_vs_reference_cpu_extension():
+    """[4,128,8,64] fp32 through the real consumer chain -- L1Attn -> softmax over dim 1 ->
+    einsum('bsdh,bshw->bdhw') with v -> backward(g) -- against the same chain on the reference's CPU
+    extension (cpp/l1attn_drv.cpp compiled into oracle/_ref; float64-only, so it gets float64 casts of the
+    same seeded values), else on the C restatement of that extension."""
+    import os
+    import sys
+    from conftest import ROOT
+    import l1attn_cuda
+    gen = torch.Generator().manual_seed(1001)
+    q, k, v, g = (torch.randn(4, 128, 8, 64, generator=gen) for _ in range(4))
+    refdir = os.path.join(ROOT, "oracle", "_ref")
+    if os.path.exists(os.path.join(refdir, "l1attn_drv_cpp.so")):
+        if refdir not in sys.path:
+            sys.path.insert(0, refdir)
+        import l1attn_drv_cpp
+        fwd = lambda a, b: l1attn_drv_cpp.forward(a, b)[0]
+        bwd = lambda d, a, b: l1attn_drv_cpp.backward(d, a, b)
+    else:
+        from oracle import oracle
+        fwd = lambda a, b: torch.from_numpy(oracle.dense_fwd(a.numpy(), b.numpy()))
+        bwd = lambda d, a, b: [torch.from_numpy(x) for x in oracle.dense_bwd(d.numpy(), a.numpy(), b.numpy())]
+
+    class CpuFn(torch.autograd.Function):  # the glue of cpp/l1attn_cpp.py:8-27
+        @staticmethod
+        def forward(ctx, a, b):
+            ctx.save_for_backward(a, b)
+            return fwd(a.contiguous(), b.contiguous())
+
+        @staticmethod
+        def backward(ctx, d):
+            return tuple(bwd(d.contiguous(), *ctx.saved_tensors))
+
+    def chain(op, q_, k_, v_, g_):
+        q_, k_, v_ = (t.clone().requires_grad_(True) for t in (q_, k_, v_))
+        vo = torch.einsum("bsdh,bshw->bdhw", torch.softmax(op(q_, k_), 1), v_)
+        vo.backward(g_)
+        return [vo.detach(), q_.grad, k_.grad, v_.grad]
+
+    want = chain(CpuFn.apply, q.double(), k.double(), v.double(), g.double())
+    got = chain(l1attn_cuda.L1Attn(), q.cuda(), k.cuda(), v.cuda(), g.cuda())
+    for a, b, name in zip(got, want, ("vo", "d_q", "d_k", "d_v")):
+        assert_close(a.cpu().numpy(), b.numpy(), 1e-5, "config-1 chain " + name)
+
+
+@pytest.mark.parametrize("script", ["check.py", "check_sparse.py"])
+def test_reference_check_scripts_run_unmodified(script):
+    """The reference's own acceptance scripts, unmodified, with this library's modules standing in for
+    its l1attn_cuda / l1attn_sparse_cuda / l1attn_sparse_bidi_cuda (same module and class names) and its
+    CPU extension taken from oracle/_ref.  They need a checkout of the reference (L1ATTN_REFERENCE) beside
+    a GPU; where there is none the test is skipped -- the scripts are not copied into this repository."""
+    import os
+    import subprocess
+    import sys
+    import textwrap
+    from conftest import ROOT, PKG
+    ref = os.environ.get("L1ATTN_REFERENCE", "")
+    if not ref or not os.path.exists(os.path.join(ref, script)):
+        pytest.skip("no checkout of the reference here (set L1ATTN_REFERENCE): its scripts are not vendored")
+    refso = os.path.join(ROOT, "oracle", "_ref")
+    if not os.path.exists(os.path.join(refso, "l1attn_sparse_drv.so")):
+        pytest.skip("reference CPU extension not built (oracle/build_ref.py)")
+    # the reference's thin Python wrappers of its CPU extension live in <ref>/cpp; matplotlib is not installed
+    # here and check.py imports it only to plot, so an empty stand-in module is put on the path
+    boot = textwrap.dedent("""
+        import sys, types, runpy
+        mpl = types.ModuleType("matplotlib"); plt = types.ModuleType("matplotlib.pyplot")
+        mpl.pyplot = plt; sys.modules.setdefault("matplotlib", mpl); sys.modules.setdefault("matplotlib.pyplot", plt)
+        sys.path[:0] = [%r, %r, %r, %r]
+        runpy.run_path(%r, run_name="__main__")
+    """) % (PKG, refso, os.path.join(ref, "cpp"), ref, os.path.join(ref, script))
+    r = subprocess.run([sys.executable, "-c", boot], cwd=ref, capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]

@@ -1,4 +1,7 @@
-"""Multi-process (world_size 2 and 3, gloo, CPU) tests of the batch partitioning used for N > 1 GPUs."""
+"""Multi-process (world_size 2 and 3, gloo, CPU) tests of the partitioning used for N > 1 GPUs: batch slices,
+(batch, head group) slabs of the dense operator, and the sparse operator by dst-token range with its one
+all-reduce of the d_k / d_v partial sums.  The compute itself is a pure-torch stand-in here (the library has no
+CPU path); what is tested is the partition, the placement of the pieces and the collectives."""
 import os
 import sys
 
@@ -58,3 +61,146 @@ def test_shard_range_errors_and_single_process():
     assert sh.max_over_ranks(3.5) == 3.5
     t = torch.ones(2, 3)
     assert sh.gather_batch(t, 2) is t
+
+
+# ------------------------------------------------------------------ (batch, head group) slabs
+
+def test_dense_partition_covers_every_batch_head_pair_once():
+    sys.path.insert(0, PKG)
+    import l1attn_shard as sh
+    for bs, heads, world in [(16, 16, 8), (2, 8, 8), (2, 8, 4), (2, 8, 2), (3, 5, 7), (1, 16, 3), (5, 4, 2)]:
+        part = sh.dense_partition(bs, heads, world)
+        assert len(part) == world
+        seen = torch.zeros(bs, heads, dtype=torch.int32)
+        for b0, b1, h0, h1 in part:
+            assert b1 > b0 and h1 > h0
+            seen[b0:b1, h0:h1] += 1
+        assert bool((seen == 1).all()), (bs, heads, world)
+    assert sh.dense_partition(2, 8, 8)[5] == (1, 2, 2, 4)        # long-context shape on 8 ranks: 2 heads each
+    assert sh.dense_partition(16, 16, 8)[3] == (6, 8, 0, 16)     # benchmark shape: 2 batch items, all heads
+    with pytest.raises(ValueError):
+        sh.dense_partition(1, 2, 3)
+
+
+def _torch_scores(q, k):
+    return -(q[:, None, :, :, :] - k[:, :, None, :, :]).abs().sum(-1) / q.shape[-1] ** 0.5  # [b, s, t, h]
+
+
+def _dense_worker(rank, world, port, shape, q):
+    sys.path.insert(0, PKG)
+    import l1attn_shard as sh
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        bs, n, h, w = shape
+        g = torch.Generator().manual_seed(3)
+        qq, kk = torch.randn(shape, generator=g), torch.randn(shape, generator=g)
+        slab = sh.dense_partition(bs, h, world)[rank]
+        local = _torch_scores(sh.dense_local(qq, slab), sh.dense_local(kk, slab))
+        full = sh.gather_dense(local, bs, h)
+        q.put((rank, bool(torch.equal(full, _torch_scores(qq, kk)))))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,shape", [(2, (4, 6, 4, 5)), (3, (2, 5, 6, 4)), (2, (1, 7, 3, 2))])
+def test_head_group_shards_assemble_to_the_global_scores(world, shape):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 31500 + (os.getpid() * 11 + world * 17 + shape[0]) % 2000
+    procs = [ctx.Process(target=_dense_worker, args=(r, world, port, shape, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = sorted(q.get(timeout=120) for _ in range(world))
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert all(ok for _, ok in res)
+
+
+# ------------------------------------------------------------------ sparse by dst-token range
+
+class _TorchSparseOps:
+    """Stand-in compute backend for SparseShard on the CPU: the operator's math in differentiable torch
+    (scatter form), the edge index replaced by the expanded list itself."""
+
+    def expand(self, co):
+        from oracle import oracle
+        coo, dm, _ = oracle.expand_coo(co.numpy())
+        return torch.from_numpy(coo), dm
+
+    def index(self, coo, n_tok, dst_mxlen):
+        return coo.long()
+
+    @staticmethod
+    def _vo(v, q, k, coo, usm):
+        dst, src = coo[:, 0], coo[:, 1]
+        x = -(q[:, dst] - k[:, src]).abs().sum(-1) / q.shape[-1] ** 0.5
+        e = torch.exp(x)
+        a = e / torch.ones_like(q[..., 0]).index_add(1, dst, e)[:, dst] if usm else e
+        return torch.zeros_like(v).index_add(1, dst, a.unsqueeze(-1) * v[:, src]), a
+
+    def forward(self, v, q, k, ix, usm, out):
+        vo, a = self._vo(v, q, k, ix, usm)
+        out[0].copy_(vo)
+        out[1].zero_()
+        out[1][:, ix[:, 0], ix[:, 2]] = a
+        return out
+
+    def backward(self, dvo, v, q, k, ix, attn, usm, out, scratch):
+        v, q, k = (t.detach().clone().requires_grad_(True) for t in (v, q, k))
+        self._vo(v, q, k, ix, usm)[0].backward(dvo)
+        for o, t in zip((out[0], out[2], out[3]), (v, q, k)):
+            o.copy_(t.grad if t.grad is not None else torch.zeros_like(t))
+
+
+def _sparse_worker(rank, world, port, bs, q):
+    sys.path.insert(0, PKG)
+    import l1attn_shard as sh
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        n, h, w = 11, 2, 4
+        g = torch.Generator().manual_seed(5)
+        co = torch.stack([torch.randint(0, n, (60,), generator=g), torch.randint(0, n, (60,), generator=g)], 1)
+        v, qq, kk, dvo = (torch.randn(bs, n, h, w, generator=g, dtype=torch.float64) for _ in range(4))
+        ops = _TorchSparseOps()
+        plan = sh.SparseShard(co, bs, n, rank, world, device="cpu", ops=ops)
+        vo, dv, dq, dk = plan.forward_backward(v, qq, kk, dvo, True)
+        whole = sh.SparseShard(co, bs, n, 0, 1, device="cpu", ops=ops)
+        rvo, rdv, rdq, rdk = whole.forward_backward(v, qq, kk, dvo, True)
+        close = lambda a, b: bool(torch.allclose(a, b, rtol=1e-12, atol=1e-12))
+        if plan.mode == "batch":
+            sl = slice(plan.b0, plan.b1)
+            ok = close(vo, rvo[sl]) and close(dv, rdv[sl]) and close(dq, rdq[sl]) and close(dk, rdk[sl])
+        else:
+            rows = slice(plan.d0, plan.d1)
+            outside = torch.ones(n, dtype=torch.bool)
+            outside[rows] = False
+            ok = (close(vo[:, rows], rvo[:, rows]) and close(dq[:, rows], rdq[:, rows])   # owned dst rows complete
+                  and float(vo[:, outside].abs().sum()) == 0 and float(dq[:, outside].abs().sum()) == 0
+                  and close(dv, rdv) and close(dk, rdk))                                  # summed over the ranks
+            ok = ok and plan.collective_note() is not None
+        q.put((rank, plan.mode, ok, plan.n_edges_local))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,bs", [(2, 1), (3, 2), (2, 4)])
+def test_sparse_dst_range_and_batch_shards(world, bs):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 33500 + (os.getpid() * 13 + world * 19 + bs) % 2000
+    procs = [ctx.Process(target=_sparse_worker, args=(r, world, port, bs, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = sorted(q.get(timeout=120) for _ in range(world))
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert all(ok for _, _, ok, _ in res), res
+    assert {m for _, m, _, _ in res} == ({"batch"} if bs >= world else {"dst"})
+    if bs < world:
+        assert sum(e for _, _, _, e in res) == 60  # every edge on exactly one rank
