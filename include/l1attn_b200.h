@@ -11,9 +11,11 @@
  *      void*, NULL = the legacy default stream) and the call returns without synchronising.
  *      They allocate nothing; scratch and index buffers are passed in by the caller.
  *   *  host-buffer entry points (l1attn_*_host): tensors are in host memory; the call copies
- *      them to the current device, runs, copies results back and synchronises.  Device memory
- *      for these calls comes from a grow-only arena per device that the library keeps until
- *      l1attn_host_release() or process exit.
+ *      them to the current device, runs, copies results back and synchronises.  The work is
+ *      pipelined one batch item at a time over three streams of the library's own, so copies in
+ *      both directions overlap the kernels.  The *_host_async forms return once everything is
+ *      enqueued; l1attn_host_sync() waits.  Device memory for these calls comes from a
+ *      grow-only arena per device that the library keeps until l1attn_host_release() or process exit.
  *
  * Tensor layouts (row-major, contiguous), identical to the reference extension:
  *   q, k, v, vf, vb, vo and their gradients : [bs][n_tok][n_heads][width]   (v*: v_width)
@@ -82,10 +84,13 @@ int l1attn_dense_fwd(const void *q, const void *k, void *attn,
  * d_q[b][t][h][w] =  scale * sum_s sign(q[b][t][h][w]-k[b][s][h][w]) * d_attn[b][s][t][h]
  * d_k[b][s][h][w] = -scale * sum_t sign(q[b][t][h][w]-k[b][s][h][w]) * d_attn[b][s][t][h]
  * with scale = -1/sqrt(width) and sign(0) = 0.  Deterministic (no atomics).
- * `scratch`: device buffer of l1attn_dense_bwd_scratch_bytes() bytes (a few KB: one flag per
- * tile, written by a detector kernel that finds exact ties q == k so that tie-free tiles can take
- * a shorter inner loop), or NULL, in which case every tile takes the exact loop (same results,
- * roughly twice the time in fp32).
+ * `scratch`: device buffer of l1attn_dense_bwd_scratch_bytes() bytes (16-byte aligned, ~100 KB), or NULL.
+ * In fp32 a detector kernel proves every exact tie q == k -- the one case the fast inner loop (compare +
+ * predicated add) gets wrong -- and writes them there as a list, which a fix kernel applies after the
+ * backward, plus one flag per tile for the case that the list overflows (zero-padded tokens, q == k:
+ * the flagged tiles then take an exact loop).  With NULL every tile takes the exact loop (same results,
+ * more than twice the time in fp32).  Contents need no initialisation and mean nothing after the call;
+ * calls that share a scratch buffer must not overlap on the GPU.
  * Replaces l1attn_cuda_drv.backward (cuda/l1attn_cuda_drv.cpp:67-104) and
  * l1attn_cuda_backward{,32,64} (cuda/l1attn_cuda_kernel.cu:559-685).
  */
@@ -216,7 +221,9 @@ int l1attn_i64_minmax(const int64_t *x, long long n, int64_t *out, void *stream)
 
 /* ------------------------------------------------------------------ host buffers -------- */
 
-/* Same operations with every tensor in HOST memory (pageable or pinned); synchronous. */
+/* Same operations with every tensor in HOST memory (pageable or pinned); synchronous.
+ * (The reference has no host-buffer form: its callers move tensors with torch's .cuda() / .cpu() around
+ * l1attn_cuda_drv.forward / backward, cuda/l1attn_cuda_drv.cpp:42-104.) */
 int l1attn_dense_fwd_host(const void *q, const void *k, void *attn,
 			  int bs, int n_tok, int n_heads, int width, int dtype);
 int l1attn_dense_softmax_v_fwd_host(const void *q, const void *k, const void *v, void *vo,
@@ -232,7 +239,31 @@ int l1attn_sparse_bwd_host(const void *dvo, const void *v, const void *vb, const
 			   void *d_v, void *d_vb, void *d_q, void *d_k,
 			   int bs, int n_tok, int n_heads, int width, int v_width, int cl, int dst_mxlen,
 			   int use_softmax, int bidi, int dtype);
-/* co int64 [cl][2] -> coo int32 [cl][4]; *dst_mxlen, *src_mxlen as expandCoo returns them. */
+/*
+ * Asynchronous forms of the four calls above: they enqueue the copies in, the kernels and the copies out and
+ * return; outputs are valid after l1attn_host_sync().  Calls enqueued before the sync work on device buffers of
+ * their own and run concurrently (a backward whose d_attn does not come from the forward enqueued before it
+ * overlaps that forward's copy back).  Host buffers must stay alive and unmodified until the sync; only pinned
+ * host memory lets the copies overlap, pageable memory still gives correct results.  A call may wait for
+ * earlier ones when the arena has to grow.  l1attn_host_sync() returns the first deferred error of the calls
+ * it waited for (L1ATTN_ERR_INDEX for an out-of-range coo row) or L1ATTN_OK.
+ */
+int l1attn_dense_fwd_host_async(const void *q, const void *k, void *attn,
+				int bs, int n_tok, int n_heads, int width, int dtype);
+int l1attn_dense_bwd_host_async(const void *d_attn, const void *q, const void *k, void *d_q, void *d_k,
+				int bs, int n_tok, int n_heads, int width, int dtype);
+int l1attn_sparse_fwd_host_async(const void *v, const void *vb, const void *q, const void *k, const int32_t *coo,
+				 void *vo, void *attn,
+				 int bs, int n_tok, int n_heads, int width, int v_width, int cl, int dst_mxlen,
+				 int use_softmax, int bidi, int dtype);
+int l1attn_sparse_bwd_host_async(const void *dvo, const void *v, const void *vb, const void *q, const void *k,
+				 const int32_t *coo, const void *attn,
+				 void *d_v, void *d_vb, void *d_q, void *d_k,
+				 int bs, int n_tok, int n_heads, int width, int v_width, int cl, int dst_mxlen,
+				 int use_softmax, int bidi, int dtype);
+int l1attn_host_sync(void);
+/* co int64 [cl][2] -> coo int32 [cl][4]; *dst_mxlen, *src_mxlen as expandCoo returns them.  Token ids must fit in
+ * int32 (else L1ATTN_ERR_SHAPE) and the counters take memory proportional to max id - min id + 1. */
 int l1attn_expand_coo_host(const int64_t *co, int cl, int32_t *coo, int *dst_mxlen, int *src_mxlen);
 /* Free the current device's arena used by the *_host entry points. */
 int l1attn_host_release(void);

@@ -1,5 +1,6 @@
 // C ABI glue: argument checks of the dense entry points, error reporting, and the host-buffer
 // entry points (copy in, run, copy out) with their per-device arena.
+#include <cstdint>
 #include <cstdio>
 #include <cstring>
 #include <mutex>
@@ -35,10 +36,27 @@ int check_dense(const void *const *ptrs, int nptr, int bs, int n_tok, int n_head
 	return L1ATTN_OK;
 }
 
-// Grow-only device arena of the *_host entry points, one per device.
+// Per-device state of the *_host entry points: a grow-only device arena, three copy/compute streams and a
+// small pinned block for values read back asynchronously.
+// Every call takes fresh slices of the arena (bump allocation), so calls enqueued one after the other without
+// a synchronisation in between never share device buffers and can run concurrently; l1attn_host_sync() waits
+// for all of them and makes the whole arena available again.
+constexpr int NPIPE = 3;  // streams one call rotates its batch items over
+constexpr int NBANK = 1;  // banks of streams that consecutive calls would alternate between.  Two banks let an independent
+                          // backward's copies in run beside the preceding forward's copies out; measured on a B200 host
+                          // (PCIe 5 x16) that was slower than one bank (45.5 vs 42.0 ms per [16,1024,16,64] step: the
+                          // link moves ~60 GB/s in total whichever way the traffic is split), so one bank it is
+constexpr int NSTAT = 64;
 struct Arena {
 	void *base = nullptr;
 	size_t cap = 0, used = 0;
+	cudaStream_t all[NPIPE * NBANK] = {};
+	cudaStream_t *st = all; // the bank of the current call
+	int bank = 0;
+	cudaEvent_t ev = nullptr;
+	int32_t *stat = nullptr; // pinned, NSTAT words
+	int nstat = 0;
+	bool ready = false;
 };
 std::mutex g_mu;
 std::vector<Arena> g_arena;
@@ -53,16 +71,57 @@ Arena *arena_for_current(int *rc)
 	}
 	if (size_t(dev) >= g_arena.size())
 		g_arena.resize(dev + 1);
-	return &g_arena[dev];
+	Arena *a = &g_arena[dev];
+	if (!a->ready) {
+		for (int i = 0; i < NPIPE * NBANK && e == cudaSuccess; i++)
+			e = cudaStreamCreateWithFlags(&a->all[i], cudaStreamNonBlocking);
+		if (e == cudaSuccess)
+			e = cudaEventCreateWithFlags(&a->ev, cudaEventDisableTiming);
+		if (e == cudaSuccess)
+			e = cudaHostAlloc(reinterpret_cast<void **>(&a->stat), NSTAT * sizeof(int32_t), cudaHostAllocDefault);
+		if (e != cudaSuccess) {
+			*rc = cuda_fail(e);
+			return nullptr;
+		}
+		a->ready = true;
+	}
+	a->st = a->all + a->bank * NPIPE; // (the vector may have moved the object since the last call)
+	return a;
 }
 
-int arena_reserve(Arena *a, size_t bytes)
+// Waits for everything the *_host calls have enqueued on this device; returns the first deferred status
+// (an out-of-range coo row found by an index build) and makes the arena's memory available again.
+int arena_sync(Arena *a)
 {
+	for (int i = 0; i < NPIPE * NBANK; i++)
+		L1B_CUDA(cudaStreamSynchronize(a->all[i]));
+	int rc = L1ATTN_OK;
+	for (int i = 0; i < a->nstat; i++)
+		if (a->stat[i] != 0 && rc == L1ATTN_OK)
+			rc = a->stat[i];
+	a->nstat = 0;
 	a->used = 0;
+	return rc;
+}
+
+size_t pad256(size_t n) { return (n + 255) / 256 * 256; }
+
+// Makes `bytes` more bytes available.  When the arena has to grow, or has no room left for a deferred status
+// word, everything in flight is waited for first (earlier asynchronous calls then simply finish early);
+// *deferred receives their status.
+int arena_reserve(Arena *a, size_t bytes, int *deferred)
+{
+	*deferred = L1ATTN_OK;
+	a->bank = (a->bank + 1) % NBANK;
+	a->st = a->all + a->bank * NPIPE;
+	if (a->used + bytes <= a->cap && a->nstat < NSTAT)
+		return L1ATTN_OK;
+	*deferred = arena_sync(a);
+	if (*deferred == L1ATTN_ERR_CUDA)
+		return *deferred;
 	if (bytes <= a->cap)
 		return L1ATTN_OK;
 	if (a->base) {
-		L1B_CUDA(cudaDeviceSynchronize());
 		L1B_CUDA(cudaFree(a->base));
 		a->base = nullptr;
 		a->cap = 0;
@@ -72,14 +131,15 @@ int arena_reserve(Arena *a, size_t bytes)
 	return L1ATTN_OK;
 }
 
-size_t pad256(size_t n) { return (n + 255) / 256 * 256; }
-
 void *arena_take(Arena *a, size_t bytes)
 {
 	void *p = static_cast<unsigned char *>(a->base) + a->used;
 	a->used += pad256(bytes ? bytes : 1);
 	return p;
 }
+
+inline const void *off(const void *p, size_t bytes) { return static_cast<const unsigned char *>(p) + bytes; }
+inline void *off(void *p, size_t bytes) { return static_cast<unsigned char *>(p) + bytes; }
 
 } // namespace
 } // namespace l1b
@@ -162,35 +222,62 @@ extern "C" int l1attn_dense_bwd(const void *d_attn, const void *q, const void *k
 }
 
 // ---------------------------------------------------------------- host-buffer entry points
+//
+// One batch item at a time, the items dealt out over the three streams in rotation: while item b computes, item
+// b+1's inputs cross PCIe in one direction and item b-1's results in the other.  The *_async forms return once
+// everything is enqueued; the plain forms add l1attn_host_sync().
 
-#define H2D(dst, src, n) L1B_CUDA(cudaMemcpyAsync(dst, src, n, cudaMemcpyHostToDevice, 0))
-#define D2H(dst, src, n) L1B_CUDA(cudaMemcpyAsync(dst, src, n, cudaMemcpyDeviceToHost, 0))
+#define H2D(dst, src, n, st) L1B_CUDA(cudaMemcpyAsync(dst, src, n, cudaMemcpyHostToDevice, st))
+#define D2H(dst, src, n, st) L1B_CUDA(cudaMemcpyAsync(dst, src, n, cudaMemcpyDeviceToHost, st))
 
-extern "C" int l1attn_dense_fwd_host(const void *q, const void *k, void *attn, int bs, int n_tok, int n_heads,
-				      int width, int dtype)
+extern "C" int l1attn_host_sync(void)
+{
+	int rc = L1ATTN_OK;
+	std::lock_guard<std::mutex> lock(g_mu);
+	Arena *ar = arena_for_current(&rc);
+	if (!ar)
+		return rc;
+	return arena_sync(ar);
+}
+
+// keeps the first error of an asynchronous call and of the deferred statuses it had to collect on the way
+static int first_error(int a, int b) { return a != L1ATTN_OK ? a : b; }
+
+extern "C" int l1attn_dense_fwd_host_async(const void *q, const void *k, void *attn, int bs, int n_tok, int n_heads,
+					    int width, int dtype)
 {
 	const void *ptrs[] = {q, k, attn};
 	int rc = check_dense(ptrs, 3, bs, n_tok, n_heads, width, dtype);
 	if (rc)
 		return rc;
 	const size_t es = dtype == L1ATTN_F64 ? 8 : 4;
-	const size_t nqk = size_t(bs) * n_tok * n_heads * width * es, na = size_t(bs) * n_tok * n_tok * n_heads * es;
-	if (na == 0)
+	const size_t nqk = size_t(n_tok) * n_heads * width * es, na = size_t(n_tok) * n_tok * n_heads * es; // per batch item
+	if (na == 0 || bs == 0)
 		return L1ATTN_OK;
 	std::lock_guard<std::mutex> lock(g_mu);
 	Arena *ar = arena_for_current(&rc);
 	if (!ar)
 		return rc;
-	if ((rc = arena_reserve(ar, 2 * pad256(nqk) + pad256(na))))
+	int deferred;
+	if ((rc = arena_reserve(ar, size_t(bs) * (2 * pad256(nqk) + pad256(na)), &deferred)))
 		return rc;
-	void *dq = arena_take(ar, nqk), *dk = arena_take(ar, nqk), *da = arena_take(ar, na);
-	H2D(dq, q, nqk);
-	H2D(dk, k, nqk);
-	if ((rc = dense_fwd_launch(dq, dk, da, bs, n_tok, n_heads, width, dtype, 0)))
-		return rc;
-	D2H(attn, da, na);
-	L1B_CUDA(cudaStreamSynchronize(0));
-	return L1ATTN_OK;
+	for (int b = 0; b < bs; b++) {
+		cudaStream_t st = ar->st[b % NPIPE];
+		void *dq = arena_take(ar, nqk), *dk = arena_take(ar, nqk), *da = arena_take(ar, na);
+		H2D(dq, off(q, b * nqk), nqk, st);
+		H2D(dk, off(k, b * nqk), nqk, st);
+		if ((rc = dense_fwd_launch(dq, dk, da, 1, n_tok, n_heads, width, dtype, st)))
+			return rc;
+		D2H(off(attn, b * na), da, na, st);
+	}
+	return deferred;
+}
+
+extern "C" int l1attn_dense_fwd_host(const void *q, const void *k, void *attn, int bs, int n_tok, int n_heads,
+				      int width, int dtype)
+{
+	const int rc = l1attn_dense_fwd_host_async(q, k, attn, bs, n_tok, n_heads, width, dtype);
+	return first_error(rc, l1attn_host_sync());
 }
 
 extern "C" int l1attn_dense_softmax_v_fwd_host(const void *q, const void *k, const void *v, void *vo, int bs, int n_tok,
@@ -203,68 +290,105 @@ extern "C" int l1attn_dense_softmax_v_fwd_host(const void *q, const void *k, con
 	if (v_width < 1 || mode < L1ATTN_SV_SOFTMAX || mode > L1ATTN_SV_EXP)
 		return L1ATTN_ERR_ARG;
 	const size_t es = dtype == L1ATTN_F64 ? 8 : 4;
-	const size_t nqk = size_t(bs) * n_tok * n_heads * width * es, nv = size_t(bs) * n_tok * n_heads * v_width * es;
-	if (nv == 0)
+	const size_t nqk = size_t(n_tok) * n_heads * width * es, nv = size_t(n_tok) * n_heads * v_width * es;
+	if (nv == 0 || bs == 0)
 		return L1ATTN_OK;
-	std::lock_guard<std::mutex> lock(g_mu);
-	Arena *ar = arena_for_current(&rc);
-	if (!ar)
-		return rc;
-	if ((rc = arena_reserve(ar, 2 * pad256(nqk) + 2 * pad256(nv))))
-		return rc;
-	void *dq = arena_take(ar, nqk), *dk = arena_take(ar, nqk), *dv = arena_take(ar, nv), *dvo = arena_take(ar, nv);
-	H2D(dq, q, nqk);
-	H2D(dk, k, nqk);
-	H2D(dv, v, nv);
-	if ((rc = dense_softmax_v_launch(dq, dk, dv, dvo, nullptr, bs, n_tok, n_heads, width, v_width, mode, dtype, 0)))
-		return rc;
-	D2H(vo, dvo, nv);
-	L1B_CUDA(cudaStreamSynchronize(0));
-	return L1ATTN_OK;
+	int deferred;
+	{
+		std::lock_guard<std::mutex> lock(g_mu);
+		Arena *ar = arena_for_current(&rc);
+		if (!ar)
+			return rc;
+		if ((rc = arena_reserve(ar, size_t(bs) * (2 * pad256(nqk) + 2 * pad256(nv)), &deferred)))
+			return rc;
+		for (int b = 0; b < bs; b++) {
+			cudaStream_t st = ar->st[b % NPIPE];
+			void *dq = arena_take(ar, nqk), *dk = arena_take(ar, nqk), *dv = arena_take(ar, nv), *dvo = arena_take(ar, nv);
+			H2D(dq, off(q, b * nqk), nqk, st);
+			H2D(dk, off(k, b * nqk), nqk, st);
+			H2D(dv, off(v, b * nv), nv, st);
+			if ((rc = dense_softmax_v_launch(dq, dk, dv, dvo, nullptr, 1, n_tok, n_heads, width, v_width, mode, dtype, st)))
+				return rc;
+			D2H(off(vo, b * nv), dvo, nv, st);
+		}
+	}
+	return first_error(deferred, l1attn_host_sync());
 }
 
-extern "C" int l1attn_dense_bwd_host(const void *d_attn, const void *q, const void *k, void *d_q, void *d_k, int bs,
-				      int n_tok, int n_heads, int width, int dtype)
+extern "C" int l1attn_dense_bwd_host_async(const void *d_attn, const void *q, const void *k, void *d_q, void *d_k, int bs,
+					    int n_tok, int n_heads, int width, int dtype)
 {
 	const void *ptrs[] = {d_attn, q, k, d_q, d_k};
 	int rc = check_dense(ptrs, 5, bs, n_tok, n_heads, width, dtype);
 	if (rc)
 		return rc;
 	const size_t es = dtype == L1ATTN_F64 ? 8 : 4;
-	const size_t nqk = size_t(bs) * n_tok * n_heads * width * es, na = size_t(bs) * n_tok * n_tok * n_heads * es;
-	if (na == 0)
+	const size_t nqk = size_t(n_tok) * n_heads * width * es, na = size_t(n_tok) * n_tok * n_heads * es;
+	if (na == 0 || bs == 0)
 		return L1ATTN_OK;
 	std::lock_guard<std::mutex> lock(g_mu);
 	Arena *ar = arena_for_current(&rc);
 	if (!ar)
 		return rc;
-	const size_t nsc = dense_bwd_scratch_bytes(bs, n_tok, n_heads, width, dtype);
-	if ((rc = arena_reserve(ar, 4 * pad256(nqk) + pad256(na) + pad256(nsc))))
+	const size_t nsc = dense_bwd_scratch_bytes(1, n_tok, n_heads, width, dtype);
+	int deferred;
+	if ((rc = arena_reserve(ar, size_t(bs) * (4 * pad256(nqk) + pad256(na) + pad256(nsc)), &deferred)))
 		return rc;
-	void *dq = arena_take(ar, nqk), *dk = arena_take(ar, nqk), *dg = arena_take(ar, na);
-	void *ddq = arena_take(ar, nqk), *ddk = arena_take(ar, nqk), *dsc = arena_take(ar, nsc);
-	H2D(dq, q, nqk);
-	H2D(dk, k, nqk);
-	H2D(dg, d_attn, na);
-	if ((rc = dense_bwd_launch(dg, dq, dk, ddq, ddk, dsc, bs, n_tok, n_heads, width, dtype, 0)))
+	for (int b = 0; b < bs; b++) {
+		cudaStream_t st = ar->st[b % NPIPE];
+		void *dq = arena_take(ar, nqk), *dk = arena_take(ar, nqk), *dg = arena_take(ar, na);
+		void *ddq = arena_take(ar, nqk), *ddk = arena_take(ar, nqk), *dsc = arena_take(ar, nsc);
+		H2D(dq, off(q, b * nqk), nqk, st);
+		H2D(dk, off(k, b * nqk), nqk, st);
+		H2D(dg, off(d_attn, b * na), na, st);
+		if ((rc = dense_bwd_launch(dg, dq, dk, ddq, ddk, dsc, 1, n_tok, n_heads, width, dtype, st)))
+			return rc;
+		D2H(off(d_q, b * nqk), ddq, nqk, st);
+		D2H(off(d_k, b * nqk), ddk, nqk, st);
+	}
+	return deferred;
+}
+
+extern "C" int l1attn_dense_bwd_host(const void *d_attn, const void *q, const void *k, void *d_q, void *d_k, int bs,
+				      int n_tok, int n_heads, int width, int dtype)
+{
+	const int rc = l1attn_dense_bwd_host_async(d_attn, q, k, d_q, d_k, bs, n_tok, n_heads, width, dtype);
+	return first_error(rc, l1attn_host_sync());
+}
+
+// coo -> device, edge index built on the first stream; the other streams wait for it.  The status word of the
+// index build (an out-of-range row) is read back into the pinned block and reported by the next l1attn_host_sync().
+static int host_index(Arena *ar, const int32_t *coo, int cl, int n_tok, int dst_mxlen, void **dix)
+{
+	const size_t nc = size_t(cl) * 16, nix = l1attn_sparse_index_bytes(cl, n_tok, dst_mxlen);
+	void *dc = arena_take(ar, nc);
+	*dix = arena_take(ar, nix);
+	int32_t *dstat = static_cast<int32_t *>(arena_take(ar, 4));
+	if (cl)
+		H2D(dc, coo, nc, ar->st[0]);
+	int rc = l1attn_sparse_build_index(static_cast<int32_t *>(dc), cl, n_tok, dst_mxlen, *dix, dstat, ar->st[0]);
+	if (rc)
 		return rc;
-	D2H(d_q, ddq, nqk);
-	D2H(d_k, ddk, nqk);
-	L1B_CUDA(cudaStreamSynchronize(0));
+	int32_t *hstat = &ar->stat[ar->nstat++];
+	*hstat = 0;
+	D2H(hstat, dstat, 4, ar->st[0]);
+	L1B_CUDA(cudaEventRecord(ar->ev, ar->st[0]));
+	for (int i = 1; i < NPIPE; i++)
+		L1B_CUDA(cudaStreamWaitEvent(ar->st[i], ar->ev, 0));
 	return L1ATTN_OK;
 }
 
-extern "C" int l1attn_sparse_fwd_host(const void *v, const void *vb, const void *q, const void *k,
-				       const int32_t *coo, void *vo, void *attn, int bs, int n_tok, int n_heads,
-				       int width, int v_width, int cl, int dst_mxlen, int use_softmax, int bidi, int dtype)
+extern "C" int l1attn_sparse_fwd_host_async(const void *v, const void *vb, const void *q, const void *k,
+					     const int32_t *coo, void *vo, void *attn, int bs, int n_tok, int n_heads,
+					     int width, int v_width, int cl, int dst_mxlen, int use_softmax, int bidi, int dtype)
 {
 	if (bs < 0 || n_tok < 0 || n_heads < 0 || width < 1 || v_width < 1 || cl < 0 || dst_mxlen < 0 ||
 	    (dtype != L1ATTN_F32 && dtype != L1ATTN_F64))
 		return L1ATTN_ERR_ARG;
 	const size_t es = dtype == L1ATTN_F64 ? 8 : 4;
-	const size_t nqk = size_t(bs) * n_tok * n_heads * width * es, nv = size_t(bs) * n_tok * n_heads * v_width * es;
-	const size_t na = size_t(bs) * n_tok * dst_mxlen * n_heads * es, nc = size_t(cl) * 16;
-	if (nv == 0)
+	const size_t nqk = size_t(n_tok) * n_heads * width * es, nv = size_t(n_tok) * n_heads * v_width * es;
+	const size_t na = size_t(n_tok) * dst_mxlen * n_heads * es, nc = size_t(cl) * 16; // per batch item
+	if (nv == 0 || bs == 0)
 		return L1ATTN_OK;
 	if (!v || !q || !k || !vo || (na && !attn) || (cl && !coo) || (bidi && !vb))
 		return L1ATTN_ERR_ARG;
@@ -274,44 +398,53 @@ extern "C" int l1attn_sparse_fwd_host(const void *v, const void *vb, const void 
 	Arena *ar = arena_for_current(&rc);
 	if (!ar)
 		return rc;
-	if ((rc = arena_reserve(ar, 2 * pad256(nqk) + 3 * pad256(nv) + pad256(na) + pad256(nc) + pad256(nix) + 256)))
+	int deferred;
+	if ((rc = arena_reserve(ar, size_t(bs) * (2 * pad256(nqk) + 3 * pad256(nv) + pad256(na)) + pad256(nc) + pad256(nix) + 512,
+				&deferred)))
 		return rc;
-	void *dv = arena_take(ar, nv), *dvb = arena_take(ar, nv), *dq = arena_take(ar, nqk), *dk = arena_take(ar, nqk);
-	void *dvo = arena_take(ar, nv), *da = arena_take(ar, na), *dc = arena_take(ar, nc), *dix = arena_take(ar, nix);
-	int32_t *dstat = static_cast<int32_t *>(arena_take(ar, 4));
-	H2D(dv, v, nv);
-	if (bidi)
-		H2D(dvb, vb, nv);
-	H2D(dq, q, nqk);
-	H2D(dk, k, nqk);
-	if (cl)
-		H2D(dc, coo, nc);
-	if ((rc = l1attn_sparse_build_index(static_cast<int32_t *>(dc), cl, n_tok, dst_mxlen, dix, dstat, 0)))
+	void *dix;
+	if ((rc = host_index(ar, coo, cl, n_tok, dst_mxlen, &dix)))
 		return rc;
-	if ((rc = l1attn_sparse_fwd(dv, dvb, dq, dk, dix, dvo, da, bs, n_tok, n_heads, width, v_width, cl, dst_mxlen,
-				    use_softmax, bidi, dtype, 0)))
-		return rc;
-	int32_t stat = 0;
-	D2H(vo, dvo, nv);
-	if (na)
-		D2H(attn, da, na);
-	D2H(&stat, dstat, 4);
-	L1B_CUDA(cudaStreamSynchronize(0));
-	return stat;
+	for (int b = 0; b < bs; b++) {
+		cudaStream_t st = ar->st[b % NPIPE];
+		void *dv = arena_take(ar, nv), *dvb = arena_take(ar, nv), *dq = arena_take(ar, nqk), *dk = arena_take(ar, nqk);
+		void *dvo = arena_take(ar, nv), *da = arena_take(ar, na);
+		H2D(dv, off(v, b * nv), nv, st);
+		if (bidi)
+			H2D(dvb, off(vb, b * nv), nv, st);
+		H2D(dq, off(q, b * nqk), nqk, st);
+		H2D(dk, off(k, b * nqk), nqk, st);
+		if ((rc = l1attn_sparse_fwd(dv, dvb, dq, dk, dix, dvo, da, 1, n_tok, n_heads, width, v_width, cl, dst_mxlen,
+					    use_softmax, bidi, dtype, st)))
+			return rc;
+		D2H(off(vo, b * nv), dvo, nv, st);
+		if (na)
+			D2H(off(attn, b * na), da, na, st);
+	}
+	return deferred;
 }
 
-extern "C" int l1attn_sparse_bwd_host(const void *dvo, const void *v, const void *vb, const void *q, const void *k,
-				       const int32_t *coo, const void *attn, void *d_v, void *d_vb, void *d_q,
-				       void *d_k, int bs, int n_tok, int n_heads, int width, int v_width, int cl,
-				       int dst_mxlen, int use_softmax, int bidi, int dtype)
+extern "C" int l1attn_sparse_fwd_host(const void *v, const void *vb, const void *q, const void *k,
+				       const int32_t *coo, void *vo, void *attn, int bs, int n_tok, int n_heads,
+				       int width, int v_width, int cl, int dst_mxlen, int use_softmax, int bidi, int dtype)
+{
+	const int rc = l1attn_sparse_fwd_host_async(v, vb, q, k, coo, vo, attn, bs, n_tok, n_heads, width, v_width, cl,
+						    dst_mxlen, use_softmax, bidi, dtype);
+	return first_error(rc, l1attn_host_sync());
+}
+
+extern "C" int l1attn_sparse_bwd_host_async(const void *dvo, const void *v, const void *vb, const void *q, const void *k,
+					     const int32_t *coo, const void *attn, void *d_v, void *d_vb, void *d_q,
+					     void *d_k, int bs, int n_tok, int n_heads, int width, int v_width, int cl,
+					     int dst_mxlen, int use_softmax, int bidi, int dtype)
 {
 	if (bs < 0 || n_tok < 0 || n_heads < 0 || width < 1 || v_width < 1 || cl < 0 || dst_mxlen < 0 ||
 	    (dtype != L1ATTN_F32 && dtype != L1ATTN_F64))
 		return L1ATTN_ERR_ARG;
 	const size_t es = dtype == L1ATTN_F64 ? 8 : 4;
-	const size_t nqk = size_t(bs) * n_tok * n_heads * width * es, nv = size_t(bs) * n_tok * n_heads * v_width * es;
-	const size_t na = size_t(bs) * n_tok * dst_mxlen * n_heads * es, nc = size_t(cl) * 16;
-	if (nv == 0)
+	const size_t nqk = size_t(n_tok) * n_heads * width * es, nv = size_t(n_tok) * n_heads * v_width * es;
+	const size_t na = size_t(n_tok) * dst_mxlen * n_heads * es, nc = size_t(cl) * 16;
+	if (nv == 0 || bs == 0)
 		return L1ATTN_OK;
 	if (!dvo || !v || !q || !k || !d_v || !d_q || !d_k || (na && !attn) || (cl && !coo) || (bidi && (!vb || !d_vb)))
 		return L1ATTN_ERR_ARG;
@@ -321,37 +454,47 @@ extern "C" int l1attn_sparse_bwd_host(const void *dvo, const void *v, const void
 	Arena *ar = arena_for_current(&rc);
 	if (!ar)
 		return rc;
-	if ((rc = arena_reserve(ar, 4 * pad256(nqk) + 5 * pad256(nv) + 2 * pad256(na) + pad256(nc) + pad256(nix) + 256)))
+	int deferred;
+	if ((rc = arena_reserve(ar, size_t(bs) * (4 * pad256(nqk) + 5 * pad256(nv) + 2 * pad256(na ? na : 1)) + pad256(nc) + pad256(nix) + 512,
+				&deferred)))
 		return rc;
-	void *ddvo = arena_take(ar, nv), *dv = arena_take(ar, nv), *dvb = arena_take(ar, nv);
-	void *dq = arena_take(ar, nqk), *dk = arena_take(ar, nqk), *da = arena_take(ar, na);
-	void *gdv = arena_take(ar, nv), *gdvb = arena_take(ar, nv), *gdq = arena_take(ar, nqk), *gdk = arena_take(ar, nqk);
-	void *dx = arena_take(ar, na), *dc = arena_take(ar, nc), *dix = arena_take(ar, nix);
-	int32_t *dstat = static_cast<int32_t *>(arena_take(ar, 4));
-	H2D(ddvo, dvo, nv);
-	H2D(dv, v, nv);
-	if (bidi)
-		H2D(dvb, vb, nv);
-	H2D(dq, q, nqk);
-	H2D(dk, k, nqk);
-	if (na)
-		H2D(da, attn, na);
-	if (cl)
-		H2D(dc, coo, nc);
-	if ((rc = l1attn_sparse_build_index(static_cast<int32_t *>(dc), cl, n_tok, dst_mxlen, dix, dstat, 0)))
+	void *dix;
+	if ((rc = host_index(ar, coo, cl, n_tok, dst_mxlen, &dix)))
 		return rc;
-	if ((rc = l1attn_sparse_bwd(ddvo, dv, dvb, dq, dk, dix, da, gdv, gdvb, gdq, gdk, dx, bs, n_tok, n_heads, width,
-				    v_width, cl, dst_mxlen, use_softmax, bidi, dtype, 0)))
-		return rc;
-	int32_t stat = 0;
-	D2H(d_v, gdv, nv);
-	if (bidi)
-		D2H(d_vb, gdvb, nv);
-	D2H(d_q, gdq, nqk);
-	D2H(d_k, gdk, nqk);
-	D2H(&stat, dstat, 4);
-	L1B_CUDA(cudaStreamSynchronize(0));
-	return stat;
+	for (int b = 0; b < bs; b++) {
+		cudaStream_t st = ar->st[b % NPIPE];
+		void *ddvo = arena_take(ar, nv), *dv = arena_take(ar, nv), *dvb = arena_take(ar, nv);
+		void *dq = arena_take(ar, nqk), *dk = arena_take(ar, nqk), *da = arena_take(ar, na);
+		void *gdv = arena_take(ar, nv), *gdvb = arena_take(ar, nv), *gdq = arena_take(ar, nqk), *gdk = arena_take(ar, nqk);
+		void *dx = arena_take(ar, na);
+		H2D(ddvo, off(dvo, b * nv), nv, st);
+		H2D(dv, off(v, b * nv), nv, st);
+		if (bidi)
+			H2D(dvb, off(vb, b * nv), nv, st);
+		H2D(dq, off(q, b * nqk), nqk, st);
+		H2D(dk, off(k, b * nqk), nqk, st);
+		if (na)
+			H2D(da, off(attn, b * na), na, st);
+		if ((rc = l1attn_sparse_bwd(ddvo, dv, dvb, dq, dk, dix, da, gdv, gdvb, gdq, gdk, dx, 1, n_tok, n_heads, width,
+					    v_width, cl, dst_mxlen, use_softmax, bidi, dtype, st)))
+			return rc;
+		D2H(off(d_v, b * nv), gdv, nv, st);
+		if (bidi)
+			D2H(off(d_vb, b * nv), gdvb, nv, st);
+		D2H(off(d_q, b * nqk), gdq, nqk, st);
+		D2H(off(d_k, b * nqk), gdk, nqk, st);
+	}
+	return deferred;
+}
+
+extern "C" int l1attn_sparse_bwd_host(const void *dvo, const void *v, const void *vb, const void *q, const void *k,
+				       const int32_t *coo, const void *attn, void *d_v, void *d_vb, void *d_q,
+				       void *d_k, int bs, int n_tok, int n_heads, int width, int v_width, int cl,
+				       int dst_mxlen, int use_softmax, int bidi, int dtype)
+{
+	const int rc = l1attn_sparse_bwd_host_async(dvo, v, vb, q, k, coo, attn, d_v, d_vb, d_q, d_k, bs, n_tok, n_heads,
+						    width, v_width, cl, dst_mxlen, use_softmax, bidi, dtype);
+	return first_error(rc, l1attn_host_sync());
 }
 
 extern "C" int l1attn_expand_coo_host(const int64_t *co, int cl, int32_t *coo, int *dst_mxlen, int *src_mxlen)
@@ -364,20 +507,28 @@ extern "C" int l1attn_expand_coo_host(const int64_t *co, int cl, int32_t *coo, i
 	if (!ar)
 		return rc;
 	const size_t nco = size_t(cl) * 16, ncoo = size_t(cl) * 16;
-	// first pass: key range (needs a round trip to size the counters)
-	if ((rc = arena_reserve(ar, pad256(nco) + pad256(ncoo) + 512)))
+	int deferred;
+	if ((rc = arena_reserve(ar, pad256(nco) + pad256(ncoo) + 512, &deferred)))
 		return rc;
+	if (deferred)
+		return deferred;
+	cudaStream_t st = ar->st[0];
+	const size_t mark = ar->used; // this call is synchronous: its slices are handed back before it returns
 	void *dco = arena_take(ar, nco), *dcoo = arena_take(ar, ncoo);
 	int64_t *dmm = static_cast<int64_t *>(arena_take(ar, 16));
 	int32_t *dmx = static_cast<int32_t *>(arena_take(ar, 8));
+	ar->used = mark;
+	// first pass: key range (needs a round trip to size the counters)
 	long long lo = 0, n_keys = 0;
 	if (cl) {
-		H2D(dco, co, nco);
-		if ((rc = l1attn_i64_minmax(static_cast<int64_t *>(dco), 2LL * cl, dmm, 0)))
+		H2D(dco, co, nco, st);
+		if ((rc = l1attn_i64_minmax(static_cast<int64_t *>(dco), 2LL * cl, dmm, st)))
 			return rc;
 		int64_t mm[2];
-		D2H(mm, dmm, 16);
-		L1B_CUDA(cudaStreamSynchronize(0));
+		D2H(mm, dmm, 16, st);
+		L1B_CUDA(cudaStreamSynchronize(st));
+		if (mm[0] < INT32_MIN || mm[1] > INT32_MAX)
+			return L1ATTN_ERR_SHAPE; // the expanded list is int32, as the reference's is
 		lo = mm[0];
 		n_keys = mm[1] - mm[0] + 1;
 	}
@@ -385,18 +536,20 @@ extern "C" int l1attn_expand_coo_host(const int64_t *co, int cl, int32_t *coo, i
 	const size_t ncnt = l1attn_expand_coo_scratch_bytes(n_keys);
 	if (ncnt)
 		L1B_CUDA(cudaMalloc(&cnt, ncnt)); // rare: more than 51200 distinct token ids
-	rc = l1attn_expand_coo(static_cast<int64_t *>(dco), cl, static_cast<int32_t *>(dcoo), dmx, lo, n_keys, cnt, 0);
+	rc = l1attn_expand_coo(static_cast<int64_t *>(dco), cl, static_cast<int32_t *>(dcoo), dmx, lo, n_keys, cnt, st);
 	int32_t mx[2] = {1, 1};
 	if (!rc) {
 		cudaError_t e = cudaSuccess;
 		if (cl)
-			e = cudaMemcpyAsync(coo, dcoo, ncoo, cudaMemcpyDeviceToHost, 0);
+			e = cudaMemcpyAsync(coo, dcoo, ncoo, cudaMemcpyDeviceToHost, st);
 		if (e == cudaSuccess)
-			e = cudaMemcpyAsync(mx, dmx, 8, cudaMemcpyDeviceToHost, 0);
+			e = cudaMemcpyAsync(mx, dmx, 8, cudaMemcpyDeviceToHost, st);
 		if (e == cudaSuccess)
-			e = cudaStreamSynchronize(0);
+			e = cudaStreamSynchronize(st);
 		if (e != cudaSuccess)
 			rc = cuda_fail(e);
+	} else {
+		(void)cudaStreamSynchronize(st);
 	}
 	if (cnt)
 		cudaFree(cnt);
@@ -412,10 +565,12 @@ extern "C" int l1attn_host_release(void)
 	Arena *ar = arena_for_current(&rc);
 	if (!ar)
 		return rc;
+	rc = arena_sync(ar);
 	if (ar->base) {
 		L1B_CUDA(cudaDeviceSynchronize());
 		L1B_CUDA(cudaFree(ar->base));
 	}
-	*ar = Arena();
-	return L1ATTN_OK;
+	ar->base = nullptr;
+	ar->cap = 0;
+	return rc;
 }

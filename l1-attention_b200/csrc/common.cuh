@@ -69,10 +69,13 @@ int dense_fwd_launch(const void *q, const void *k, void *attn, int bs, int n_tok
 // fast paths: return 1 when they do not apply to the given shape / alignment / device
 int dense_fwd_tma_launch(const void *q, const void *k, void *attn, int bs, int n_tok, int n_heads, int width,
 			 int dtype, cudaStream_t st);
+// tie_hdr: device tie header {count, overflow} or nullptr.  With a header whose overflow word is 0 every tile takes the
+// compare form (the listed ties are repaired afterwards by dense_tiefix_launch); otherwise the flags decide.
 int dense_bwd_tma_launch(const void *d_attn, const void *q, const void *k, void *d_q, void *d_k, int bs, int n_tok,
-			 int n_heads, int width, int dtype, const unsigned char *exact_flags, cudaStream_t st);
-size_t dense_bwd_tma_flag_count(int bs, int n_tok, int n_heads, int width);
-int dense_ties_launch(const float *q, const float *k, unsigned char *flags, int bs, int n_tok, int n_heads, int width,
+			 int n_heads, int width, int dtype, const unsigned char *exact_flags, const int *tie_hdr, cudaStream_t st);
+int dense_tiefix_launch(const void *d_attn, void *d_q, void *d_k, const unsigned char *scratch, int bs, int n_tok,
+			int n_heads, int width, cudaStream_t st);
+int dense_ties_launch(const float *q, const float *k, unsigned char *scratch, int bs, int n_tok, int n_heads, int width,
 		      cudaStream_t st);
 // scratch: dense_bwd_scratch_bytes() bytes of device memory, or nullptr (then every tile runs the exact loop)
 int dense_bwd_launch(const void *d_attn, const void *q, const void *k, void *d_q, void *d_k, void *scratch, int bs,

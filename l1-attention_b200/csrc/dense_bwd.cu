@@ -10,6 +10,7 @@
 // thread in a fixed order: no atomics, bit-reproducible.
 #include <cstdlib>
 #include "common.cuh"
+#include "dense_bwd_tiles.h"
 
 namespace l1b {
 namespace {
@@ -176,7 +177,7 @@ size_t dense_bwd_scratch_bytes(int bs, int n_tok, int n_heads, int width, int dt
 {
 	if (dtype != L1ATTN_F32 || bs <= 0 || n_tok <= 0 || n_heads <= 0 || width <= 0)
 		return 16;
-	return ((dense_bwd_tma_flag_count(bs, n_tok, n_heads, width) + 255) / 256) * 256; // tie flags of the fast path
+	return bwd_scratch_layout(bs, n_tok, n_heads, width).bytes; // tie flags, tie header, tie list
 }
 
 int dense_bwd_launch(const void *d_attn, const void *q, const void *k, void *d_q, void *d_k, void *scratch, int bs,
@@ -186,20 +187,31 @@ int dense_bwd_launch(const void *d_attn, const void *q, const void *k, void *d_q
 		return L1ATTN_OK;
 	static const bool no_tma = getenv("L1ATTN_NO_TMA") != nullptr; // debugging aid: force the generic kernel
 	if (!no_tma) {
-		// per-tile tie flags let tie-free tiles use the two-instruction form; without scratch
-		// (or when the detector does not apply) every tile runs the exact loop
+		// With scratch the tie detector runs first: it lists every exact tie q == k (and marks tiles, for the case
+		// that the list overflows -- a device-side fact, no host round trip).  The fast kernel then takes the
+		// compare form on every tile and the listed terms are repaired afterwards; on overflow it runs the exact
+		// loop where flagged tiles meet.  Without scratch (or when the detector does not apply) every tile
+		// runs the exact loop.
 		unsigned char *flags = nullptr;
-		if (scratch && dtype == L1ATTN_F32 && width % 4 == 0 && n_heads % 4 == 0) {
+		const int *tie_hdr = nullptr;
+		if (scratch && dtype == L1ATTN_F32 && width % 4 == 0 && n_heads % 4 == 0 && aligned(scratch, 16)) {
 			const int trc = dense_ties_launch((const float *)q, (const float *)k, (unsigned char *)scratch, bs, n_tok,
 							  n_heads, width, st);
 			if (trc < 0)
 				return trc;
-			if (trc == 0)
-				flags = (unsigned char *)scratch;
+			if (trc == 0) {
+				const BwdScratchLayout sl = bwd_scratch_layout(bs, n_tok, n_heads, width);
+				flags = (unsigned char *)scratch + sl.flags;
+				tie_hdr = (const int *)((unsigned char *)scratch + sl.hdr);
+			}
 		}
-		const int rc = dense_bwd_tma_launch(d_attn, q, k, d_q, d_k, bs, n_tok, n_heads, width, dtype, flags, st);
-		if (rc <= 0)
+		const int rc = dense_bwd_tma_launch(d_attn, q, k, d_q, d_k, bs, n_tok, n_heads, width, dtype, flags, tie_hdr, st);
+		if (rc < 0)
 			return rc;
+		if (rc == 0)
+			return tie_hdr ? dense_tiefix_launch(d_attn, d_q, d_k, (const unsigned char *)scratch, bs, n_tok, n_heads,
+							     width, st)
+				       : L1ATTN_OK;
 	}
 	if (dtype == L1ATTN_F32)
 		return launch<float, 8, 4, 2>((const float *)d_attn, (const float *)q, (const float *)k, (float *)d_q,

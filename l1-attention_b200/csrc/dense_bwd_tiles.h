@@ -35,4 +35,24 @@ inline BwdFlagLayout bwd_flag_layout(int bs, int n_tok, int n_heads, int width)
 	l.ny = (n_tok + BWD_TY - 1) / BWD_TY;
 	return l;
 }
+
+// ---- listed ties ----
+constexpr int BWD_TIE_CAP = 4096; // listed ties per call; more set the overflow word and the flagged exact loops run
+
+// Caller-provided scratch of the dense backward, in this order (every part 256-byte aligned):
+//   tie flags | tie header {count, overflow} | tie list uint4[BWD_TIE_CAP]
+// The flags and the header are adjacent so that one memset clears both.
+struct BwdScratchLayout {
+	size_t flags, hdr, ties, bytes; // offsets, total
+};
+inline BwdScratchLayout bwd_scratch_layout(int bs, int n_tok, int n_heads, int width)
+{
+	auto pad = [](size_t n) { return (n + 255) / 256 * 256; };
+	BwdScratchLayout l;
+	l.flags = 0;
+	l.hdr = pad(bwd_flag_layout(bs, n_tok, n_heads, width).bytes());
+	l.ties = l.hdr + 256;
+	l.bytes = l.ties + size_t(BWD_TIE_CAP) * 16;
+	return l;
+}
 } // namespace l1b

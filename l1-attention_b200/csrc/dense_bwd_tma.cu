@@ -144,8 +144,11 @@ dense_bwd_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_cons
 		     const __grid_constant__ CUtensorMap gmap0, const __grid_constant__ CUtensorMap gmap1,
 		     const float *__restrict__ q, const float *__restrict__ k, float *__restrict__ d_q,
 		     float *__restrict__ d_k, const unsigned char *__restrict__ flags, BwdFlagLayout fl, int n_tok,
-		     int n_heads, int width, float scale, BwdWork wk, int *err)
+		     int n_heads, int width, float scale, BwdWork wk, const int *__restrict__ tie_hdr, int *err)
 {
+	// Every tie of this call is in the detector's list (no overflow): all tiles take the compare form and the fix
+	// kernel repairs the listed terms afterwards.  Otherwise the per-tile flags choose the exact loop.
+	const int listed = (tie_hdr != nullptr && tie_hdr[1] == 0) ? 1 : 0;
 	extern __shared__ __align__(1024) unsigned char smem_raw[];
 	// 1024-byte alignment by OFFSET into the shared array: a pointer rebuilt from an integer loses its
 	// address space and every access through it becomes a generic load, which measured ~2x slower here
@@ -236,7 +239,9 @@ dense_bwd_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_cons
 		// (this warp's 4 x rows and its 32 width columns; the flag arrays are padded to whole tiles and slices)
 		int xflag = 1;
 		const unsigned char *yflags = nullptr;
-		if (flags != nullptr) {
+		if (opaque(listed) != 0) {
+			xflag = 0;
+		} else if (flags != nullptr) {
 			const BwdItem x = decode(wk, item);
 			const size_t g = fl.group(x.b, x.h0, x.w0 + wp * 16); // this warp's columns: (w % 32) / 16 == wp
 			xflag = int(flags[fl.xoff(PASS) + g * fl.nxf + size_t(x.x0 + wx * XR) / BWD_XF]);
@@ -307,7 +312,7 @@ dense_bwd_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_cons
 // Returns L1ATTN_OK, a negative error, or 1 when this path does not apply.
 // flags: device tie flags laid out by bwd_flag_layout() and filled by dense_ties_launch(), or nullptr = all exact.
 int dense_bwd_tma_launch(const void *d_attn, const void *q, const void *k, void *d_q, void *d_k, int bs, int n_tok,
-			 int n_heads, int width, int dtype, const unsigned char *flags, cudaStream_t st)
+			 int n_heads, int width, int dtype, const unsigned char *flags, const int *tie_hdr, cudaStream_t st)
 {
 	if (dtype != L1ATTN_F32)
 		return 1;
@@ -352,15 +357,9 @@ int dense_bwd_tma_launch(const void *d_attn, const void *q, const void *k, void 
 	const BwdFlagLayout fl = bwd_flag_layout(bs, n_tok, n_heads, width);
 	dense_bwd_tma_kernel<<<grid, NTHREADS, smem, st>>>(qmap, kmap, gmap0, gmap1, (const float *)q, (const float *)k,
 							    (float *)d_q, (float *)d_k, flags, fl, n_tok, n_heads, width, scale,
-							    wk, err);
+							    wk, tie_hdr, err);
 	L1B_LAUNCH_CHECK();
 	return L1ATTN_OK;
-}
-
-// bytes of tie flags the launch above reads
-size_t dense_bwd_tma_flag_count(int bs, int n_tok, int n_heads, int width)
-{
-	return bwd_flag_layout(bs, n_tok, n_heads, width).bytes();
 }
 
 } // namespace l1b

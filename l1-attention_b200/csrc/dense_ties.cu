@@ -58,7 +58,7 @@ __device__ __forceinline__ void load_batch(const float *base, size_t row, int t0
 template <int NC>
 __global__ void __launch_bounds__(NT_MAX) dense_ties_kernel(const float *__restrict__ q, const float *__restrict__ k,
 							 unsigned char *flags, int n_tok, int n_heads, int width,
-							 int log2bits, BwdFlagLayout fl)
+							 int log2bits, BwdFlagLayout fl, int *tie_hdr, uint4 *tie_list)
 {
 	extern __shared__ unsigned bitmap[]; // [NC][words]
 	__shared__ unsigned cand_bits[CAP];  // candidate value
@@ -135,6 +135,7 @@ __global__ void __launch_bounds__(NT_MAX) dense_ties_kernel(const float *__restr
 									xq[g * fl.nxf + t / BWD_XF] = 1;
 									yq[g * fl.ny + t / BWD_TY] = 1;
 									overflow = 1;
+									tie_hdr[1] = 1; // not every tie of this call gets listed
 								}
 							}
 						}
@@ -163,6 +164,13 @@ __global__ void __launch_bounds__(NT_MAX) dense_ties_kernel(const float *__restr
 						xk[g * fl.nxf + t / BWD_XF] = 1; // k row t equals a q value
 						yk[g * fl.ny + t / BWD_TY] = 1;
 						cand_hit[ci] = 1;
+						// the proven tie itself, for the fix kernel: (batch, head, column), query row, source row
+						const int idx = atomicAdd(&tie_hdr[0], 1);
+						if (idx < BWD_TIE_CAP)
+							tie_list[idx] = make_uint4((unsigned(b) * n_heads + h) * width + w0 + j,
+										   cand_where[ci] & 0xffffffu, unsigned(t), 0u);
+						else
+							tie_hdr[1] = 1;
 					}
 			}
 		}
@@ -192,7 +200,7 @@ __global__ void __launch_bounds__(NT_MAX) dense_ties_kernel(const float *__restr
 
 template <int NC>
 int launch_nc(const float *q, const float *k, unsigned char *flags, int bs, int n_tok, int n_heads, int width, int log2bits,
-	      const BwdFlagLayout &fl, cudaStream_t st)
+	      const BwdFlagLayout &fl, int *tie_hdr, uint4 *tie_list, cudaStream_t st)
 {
 	const long long grid = (long long)bs * n_heads * ((width + NC - 1) / NC);
 	if (grid > 0x7fffffffLL)
@@ -202,18 +210,89 @@ int launch_nc(const float *q, const float *k, unsigned char *flags, int bs, int 
 	int nt = 256;
 	while (nt < NT_MAX && nt * TB < n_tok)
 		nt *= 2;
-	dense_ties_kernel<NC><<<unsigned(grid), nt, smem, st>>>(q, k, flags, n_tok, n_heads, width, log2bits, fl);
+	dense_ties_kernel<NC><<<unsigned(grid), nt, smem, st>>>(q, k, flags, n_tok, n_heads, width, log2bits, fl, tie_hdr, tie_list);
 	L1B_LAUNCH_CHECK();
 	return L1ATTN_OK;
 }
 
+// Repairs the listed ties after the compare-form backward.  That form counts a term as +g where a > b and as -g
+// otherwise, so a tie q == k (which must contribute nothing) has put -scale * g into d_q[b][t][h][w] and into
+// d_k[b][s][h][w]: both get scale * g[b][s][t][h] back.
+// One CTA.  The list arrives in no particular order (the detector appends with an atomic counter), so it is
+// ranked first -- by (column, query row, source row) for d_q, by (column, source row, query row) for d_k -- and
+// every run of entries that hit the same output element is summed by one thread in rank order: the result
+// does not depend on the order of arrival.
+__global__ void __launch_bounds__(1024)
+dense_tiefix_kernel(const int *__restrict__ tie_hdr, const uint4 *__restrict__ ties, const float *__restrict__ g,
+		    float *__restrict__ d_q, float *__restrict__ d_k, int n_tok, int n_heads, int width, float scale)
+{
+	extern __shared__ __align__(16) unsigned char fix_smem[];
+	if (tie_hdr[1] != 0)
+		return; // list incomplete: the backward ran its exact loops instead
+	const int n = min(tie_hdr[0], BWD_TIE_CAP);
+	if (n == 0)
+		return;
+	uint4 *e = reinterpret_cast<uint4 *>(fix_smem);                             // {column, query row, source row, -}
+	int *perm_q = reinterpret_cast<int *>(fix_smem + size_t(BWD_TIE_CAP) * 16); // rank -> entry, d_q order
+	int *perm_k = perm_q + BWD_TIE_CAP;
+	for (int i = threadIdx.x; i < n; i += blockDim.x)
+		e[i] = ties[i];
+	__syncthreads();
+	for (int i = threadIdx.x; i < n; i += blockDim.x) {
+		const uint4 a = e[i];
+		int rq = 0, rk = 0;
+		for (int j = 0; j < n; j++) {
+			const uint4 c = e[j];
+			const bool col_lt = c.x < a.x, col_eq = c.x == a.x;
+			rq += (col_lt || (col_eq && (c.y < a.y || (c.y == a.y && c.z < a.z)))) ? 1 : 0;
+			rk += (col_lt || (col_eq && (c.z < a.z || (c.z == a.z && c.y < a.y)))) ? 1 : 0;
+		}
+		perm_q[rq] = i; // entries are distinct (column, query row, source row) triples: the ranks are a permutation
+		perm_k[rk] = i;
+	}
+	__syncthreads();
+	const size_t row = size_t(n_heads) * width;
+	const unsigned hwn = unsigned(n_heads) * unsigned(width);
+	auto gval = [&](const uint4 &a) -> float {
+		const unsigned b = a.x / hwn, hh = (a.x % hwn) / unsigned(width);
+		return g[((size_t(b) * n_tok + a.z) * n_tok + a.y) * n_heads + hh];
+	};
+	for (int p = threadIdx.x; p < n; p += blockDim.x) {
+		const uint4 a = e[perm_q[p]];
+		if (p == 0 || e[perm_q[p - 1]].x != a.x || e[perm_q[p - 1]].y != a.y) {
+			float sum = 0.f;
+			for (int pp = p; pp < n; pp++) {
+				const uint4 c = e[perm_q[pp]];
+				if (c.x != a.x || c.y != a.y)
+					break;
+				sum += gval(c);
+			}
+			d_q[(size_t(a.x / hwn) * n_tok + a.y) * row + a.x % hwn] += scale * sum;
+		}
+	}
+	for (int p = threadIdx.x; p < n; p += blockDim.x) {
+		const uint4 a = e[perm_k[p]];
+		if (p == 0 || e[perm_k[p - 1]].x != a.x || e[perm_k[p - 1]].z != a.z) {
+			float sum = 0.f;
+			for (int pp = p; pp < n; pp++) {
+				const uint4 c = e[perm_k[pp]];
+				if (c.x != a.x || c.z != a.z)
+					break;
+				sum += gval(c);
+			}
+			d_k[(size_t(a.x / hwn) * n_tok + a.z) * row + a.x % hwn] += scale * sum;
+		}
+	}
+}
+
 } // namespace
 
-// Fills the flag arrays (device, bwd_flag_layout(...).bytes() bytes).  Returns L1ATTN_OK, a negative
+// Fills the flag arrays, the tie header and the tie list in `scratch` (device, laid out by bwd_scratch_layout();
+// the d_q partials behind them are not touched).  Returns L1ATTN_OK, a negative
 // error, or 1 when the detector does not apply (token index beyond 24 bits, width not a multiple of 4,
 // q or k not 16-byte aligned);
 // the caller then runs every tile with the exact loop.
-int dense_ties_launch(const float *q, const float *k, unsigned char *flags, int bs, int n_tok, int n_heads, int width,
+int dense_ties_launch(const float *q, const float *k, unsigned char *scratch, int bs, int n_tok, int n_heads, int width,
 		      cudaStream_t st)
 {
 	if (width % 4 != 0 || n_tok >= (1 << 24))
@@ -227,9 +306,28 @@ int dense_ties_launch(const float *q, const float *k, unsigned char *flags, int 
 	int log2bits = 15;
 	while (log2bits < 18 && (1 << log2bits) < 64 * n_tok)
 		log2bits++;
+	if ((unsigned long long)bs * n_heads * width > 0xffffffffull)
+		return 1; // a tie entry holds the (batch, head, column) index in 32 bits
 	const BwdFlagLayout fl = bwd_flag_layout(bs, n_tok, n_heads, width);
-	L1B_CUDA(cudaMemsetAsync(flags, 0, fl.bytes(), st));
-	return launch_nc<4>(q, k, flags, bs, n_tok, n_heads, width, log2bits, fl, st);
+	const BwdScratchLayout sl = bwd_scratch_layout(bs, n_tok, n_heads, width);
+	L1B_CUDA(cudaMemsetAsync(scratch, 0, sl.hdr + 256, st)); // flags and header
+	return launch_nc<4>(q, k, scratch + sl.flags, bs, n_tok, n_heads, width, log2bits, fl,
+			    reinterpret_cast<int *>(scratch + sl.hdr), reinterpret_cast<uint4 *>(scratch + sl.ties), st);
+}
+
+// Enqueue after the compare-form backward: adds the listed ties' terms back (no-op when the list overflowed).
+int dense_tiefix_launch(const void *d_attn, void *d_q, void *d_k, const unsigned char *scratch, int bs, int n_tok,
+			int n_heads, int width, cudaStream_t st)
+{
+	const BwdScratchLayout sl = bwd_scratch_layout(bs, n_tok, n_heads, width);
+	const size_t smem = size_t(BWD_TIE_CAP) * (16 + 8);
+	L1B_CUDA(cudaFuncSetAttribute(dense_tiefix_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+	dense_tiefix_kernel<<<1, 1024, smem, st>>>(reinterpret_cast<const int *>(scratch + sl.hdr),
+						   reinterpret_cast<const uint4 *>(scratch + sl.ties), (const float *)d_attn,
+						   (float *)d_q, (float *)d_k, n_tok, n_heads, width,
+						   float(-1.0 / sqrt(double(width))));
+	L1B_LAUNCH_CHECK();
+	return L1ATTN_OK;
 }
 
 } // namespace l1b

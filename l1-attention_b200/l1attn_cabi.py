@@ -45,6 +45,11 @@ SIGNATURES = {
     "l1attn_dense_bwd_host": (_i, [_vp] * 5 + [_i] * 5),
     "l1attn_sparse_fwd_host": (_i, [_vp] * 7 + [_i] * 10),
     "l1attn_sparse_bwd_host": (_i, [_vp] * 11 + [_i] * 10),
+    "l1attn_dense_fwd_host_async": (_i, [_vp] * 3 + [_i] * 5),
+    "l1attn_dense_bwd_host_async": (_i, [_vp] * 5 + [_i] * 5),
+    "l1attn_sparse_fwd_host_async": (_i, [_vp] * 7 + [_i] * 10),
+    "l1attn_sparse_bwd_host_async": (_i, [_vp] * 11 + [_i] * 10),
+    "l1attn_host_sync": (_i, []),
     "l1attn_expand_coo_host": (_i, [_vp, _i, _vp, _c.POINTER(_i), _c.POINTER(_i)]),
     "l1attn_host_release": (_i, []),
 }
@@ -96,13 +101,32 @@ def _ptr(a):
     return None if a is None else a.ctypes.data
 
 
-def dense_fwd_host(q, k, out=None):
+def dense_fwd_host(q, k, out=None, wait=True):
+    """wait=False: only enqueue (l1attn_dense_fwd_host_async); the result is valid after host_sync() and the
+    arrays passed in must stay alive and unchanged until then."""
     q = _np(q)
     k = _np(k, q.dtype)
     bs, n, h, w = q.shape
     attn = np.empty((bs, n, n, h), dtype=q.dtype) if out is None else out
-    _check(lib().l1attn_dense_fwd_host(_ptr(q), _ptr(k), _ptr(attn), bs, n, h, w, _dt(q)), "l1attn_dense_fwd_host")
+    f = lib().l1attn_dense_fwd_host if wait else lib().l1attn_dense_fwd_host_async
+    _hold(wait, q, k, attn)
+    _check(f(_ptr(q), _ptr(k), _ptr(attn), bs, n, h, w, _dt(q)), "l1attn_dense_fwd_host")
     return attn
+
+
+_PENDING = []  # arrays of calls enqueued with wait=False: kept alive until host_sync()
+
+
+def _hold(wait, *arrays):
+    if not wait:
+        _PENDING.append(arrays)
+
+
+def host_sync():
+    """Wait for every *_host call enqueued with wait=False; raises the first deferred error."""
+    rc = lib().l1attn_host_sync()
+    del _PENDING[:]
+    _check(rc, "l1attn_host_sync")
 
 
 SV_MODES = {"softmax": 0, "softmax_plus_one": 1, "exp": 2}
@@ -119,17 +143,18 @@ def dense_softmax_v_fwd_host(q, k, v, mode="softmax"):
     return vo
 
 
-def dense_bwd_host(d_attn, q, k, out=None):
+def dense_bwd_host(d_attn, q, k, out=None, wait=True):
     q = _np(q)
     k, d_attn = _np(k, q.dtype), _np(d_attn, q.dtype)
     bs, n, h, w = q.shape
     dq, dk = (np.empty_like(q), np.empty_like(q)) if out is None else out
-    _check(lib().l1attn_dense_bwd_host(_ptr(d_attn), _ptr(q), _ptr(k), _ptr(dq), _ptr(dk), bs, n, h, w, _dt(q)),
-           "l1attn_dense_bwd_host")
+    f = lib().l1attn_dense_bwd_host if wait else lib().l1attn_dense_bwd_host_async
+    _hold(wait, d_attn, q, k, dq, dk)
+    _check(f(_ptr(d_attn), _ptr(q), _ptr(k), _ptr(dq), _ptr(dk), bs, n, h, w, _dt(q)), "l1attn_dense_bwd_host")
     return dq, dk
 
 
-def sparse_fwd_host(v, q, k, coo, dst_mxlen, use_softmax=True, vb=None, out=None):
+def sparse_fwd_host(v, q, k, coo, dst_mxlen, use_softmax=True, vb=None, out=None, wait=True):
     """vb given -> bidirectional operator.  Returns (vo, attn); out=(vo, attn) reuses caller arrays
     (pinned ones make the copies back run at full PCIe rate)."""
     q = _np(q)
@@ -143,13 +168,15 @@ def sparse_fwd_host(v, q, k, coo, dst_mxlen, use_softmax=True, vb=None, out=None
         attn = np.empty((bs, n, int(dst_mxlen), h), dtype=q.dtype)
     else:
         vo, attn = out
-    _check(lib().l1attn_sparse_fwd_host(_ptr(v), _ptr(vb), _ptr(q), _ptr(k), _ptr(coo), _ptr(vo), _ptr(attn),
-                                        bs, n, h, w, wv, coo.shape[0], int(dst_mxlen), int(bool(use_softmax)),
-                                        int(vb is not None), _dt(q)), "l1attn_sparse_fwd_host")
+    f = lib().l1attn_sparse_fwd_host if wait else lib().l1attn_sparse_fwd_host_async
+    _hold(wait, v, vb, q, k, coo, vo, attn)
+    _check(f(_ptr(v), _ptr(vb), _ptr(q), _ptr(k), _ptr(coo), _ptr(vo), _ptr(attn),
+             bs, n, h, w, wv, coo.shape[0], int(dst_mxlen), int(bool(use_softmax)),
+             int(vb is not None), _dt(q)), "l1attn_sparse_fwd_host")
     return vo, attn
 
 
-def sparse_bwd_host(dvo, v, q, k, coo, attn, dst_mxlen, use_softmax=True, vb=None, out=None):
+def sparse_bwd_host(dvo, v, q, k, coo, attn, dst_mxlen, use_softmax=True, vb=None, out=None, wait=True):
     """Returns (d_v, d_q, d_k) or, with vb, (d_vf, d_vb, d_q, d_k); out=(d_v, d_vb or None, d_q, d_k) reuses caller arrays."""
     q = _np(q)
     k, v, dvo, attn = _np(k, q.dtype), _np(v, q.dtype), _np(dvo, q.dtype), _np(attn, q.dtype)
@@ -162,9 +189,11 @@ def sparse_bwd_host(dvo, v, q, k, coo, attn, dst_mxlen, use_softmax=True, vb=Non
         dvb = np.empty_like(v) if vb is not None else None
     else:
         dv, dvb, dq, dk = out
-    _check(lib().l1attn_sparse_bwd_host(_ptr(dvo), _ptr(v), _ptr(vb), _ptr(q), _ptr(k), _ptr(coo), _ptr(attn),
-                                        _ptr(dv), _ptr(dvb), _ptr(dq), _ptr(dk), bs, n, h, w, wv, coo.shape[0],
-                                        int(dst_mxlen), int(bool(use_softmax)), int(vb is not None), _dt(q)),
+    f = lib().l1attn_sparse_bwd_host if wait else lib().l1attn_sparse_bwd_host_async
+    _hold(wait, dvo, v, vb, q, k, coo, attn, dv, dvb, dq, dk)
+    _check(f(_ptr(dvo), _ptr(v), _ptr(vb), _ptr(q), _ptr(k), _ptr(coo), _ptr(attn),
+             _ptr(dv), _ptr(dvb), _ptr(dq), _ptr(dk), bs, n, h, w, wv, coo.shape[0],
+             int(dst_mxlen), int(bool(use_softmax)), int(vb is not None), _dt(q)),
            "l1attn_sparse_bwd_host")
     return (dv, dq, dk) if vb is None else (dv, dvb, dq, dk)
 

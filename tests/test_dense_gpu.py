@@ -154,6 +154,15 @@ def test_host_buffer_entry_points():
     rq, rk = oracle.dense_bwd(g64, q64, k64)
     assert_close(dq, rq, 1e-5, "host dq")
     assert_close(dk, rk, 1e-5, "host dk")
+    # asynchronous forms: forward and an independent backward enqueued together, several times over (the arena
+    # has to grow and to be reused), results valid after the sync and equal to the synchronous ones
+    for rep in range(3):
+        attn2 = np.empty_like(attn)
+        dq2, dk2 = np.empty_like(dq), np.empty_like(dk)
+        cabi.dense_fwd_host(q, k, out=attn2, wait=False)
+        cabi.dense_bwd_host(g, q, k, out=(dq2, dk2), wait=False)
+        cabi.host_sync()
+        assert np.array_equal(attn2, attn) and np.array_equal(dq2, dq) and np.array_equal(dk2, dk)
     assert cabi.lib().l1attn_host_release() == 0
 
 

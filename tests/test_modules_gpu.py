@@ -254,23 +254,70 @@ def _seeded(shape, seed, scale=1.0):
     return torch.randn(shape, device="cuda", generator=gen).mul_(scale)
 
 
-@pytest.mark.parametrize("shape", [(16, 1024, 16, 64), (2, 4096, 8, 128)])
-def test_dense_fp32_vs_reference_cuda_benchmark_shapes(shape):
-    """[16,1024,16,64] takes the reference's width==64 kernels (cuda/l1attn_cuda_kernel.cu:137-203,
-    369-455), [2,4096,8,128] its width%32 kernels (:72-135, 284-367)."""
+def _agree_or_reference_race(x, r, exact_at, tol, what, racy):
+    """x (this library) against r (the reference's GPU kernel) at `tol`, norm-wise.
+
+    racy: the reference's tiled kernels for widths that are multiples of 32 other than 64 overwrite their shared
+    q/k tiles for the next 32 columns while slower warps still read the current ones (no barrier at the end of
+    the loop body, cuda/l1attn_cuda_kernel.cu:112-130 and :327-366), so for width > 32 some of ITS elements come
+    out wrong, differently on every run: a fraction of a percent of the scores, and a sizeable share of the
+    gradient elements, each of which sums hundreds of such tiles.  There the norm-wise test is applied to the
+    elements on which the two agree, and sampled elements -- disagreeing ones first -- are evaluated in float64
+    (`exact_at(index)`): this library must match it everywhere, the reference must be the one that is off where
+    they disagree."""
     from conftest import assert_close_torch
+    mx = float(r.abs().max())
+    bad = (x - r).abs() > tol * mx
+    nbad = int(bad.sum())
+    if not racy:
+        assert nbad == 0, "%s: %d of %d elements differ from the reference" % (what, nbad, x.numel())
+        assert_close_torch(x, r, tol, what)
+        return 0
+    good = ~bad
+    d = ((x - r) * good).double()
+    rms = float((d ** 2).sum().sqrt() / ((r * good).double() ** 2).sum().sqrt())
+    if nbad <= 1e-3 * x.numel():  # (a gradient whose reference is corrupted in many places has no clean remainder to test)
+        assert rms <= tol, "%s: rms-rel %.3e over the agreeing elements" % (what, rms)
+    picks = bad.nonzero()[:: max(1, nbad // 16)][:16].tolist() if nbad else []
+    gen = torch.Generator().manual_seed(9)
+    picks += [[int(torch.randint(0, n, (1,), generator=gen)) for n in x.shape] for _ in range(16)]
+    for ix in picks:
+        ix = tuple(ix)
+        want, ours, theirs = exact_at(ix), float(x[ix]), float(r[ix])
+        assert abs(ours - want) <= tol * mx, "%s %s: %.8g, float64 %.8g" % (what, ix, ours, want)
+        if bool(bad[ix]):
+            assert abs(theirs - want) > 0.5 * tol * mx, "%s %s: the reference (%.8g) is right and this library is not" % (what, ix, theirs)
+    return nbad
+
+
+@pytest.mark.parametrize("shape", [(16, 1024, 16, 64), (2, 4096, 8, 32), (2, 4096, 8, 128)])
+def test_dense_fp32_vs_reference_cuda_benchmark_shapes(shape):
+    """[16,1024,16,64] takes the reference's width==64 kernels (cuda/l1attn_cuda_kernel.cu:137-203, 369-455);
+    [2,4096,8,32] and [2,4096,8,128] its width%32 kernels (:72-135, 284-367), race-free only at width 32."""
     ref = _ref_cuda("ref_l1attn_cuda_drv")
     import l1attn_cuda_drv as new
     bs, n, h, w = shape
     q = torch.cat([_seeded((1, n, h, w), 2000 + b) for b in range(bs)])
     k = torch.cat([_seeded((1, n, h, w), 2100 + b) for b in range(bs)])
+    scale = -1.0 / w ** 0.5
     a, r = new.forward(q, k)[0], ref.forward(q, k)[0]
-    assert_close_torch(a, r, 1e-5, "attn")
+    racy = w % 32 == 0 and w > 32 and w != 64
+    _agree_or_reference_race(a, r, lambda i: scale * float((q[i[0], i[2], i[3]].double() - k[i[0], i[1], i[3]].double()).abs().sum()),
+                             1e-5, "attn", racy)
     del a, r
     g = _seeded((bs, n, n, h), 2200)
     ours, theirs = new.backward(g, q, k), ref.backward(g, q, k)
-    for x, y, name in zip(ours, theirs, ("d_q", "d_k")):
-        assert_close_torch(x, y, 1e-5, name)
+
+    def dq_at(i):  # (b, t, h, w)
+        sg = torch.sign(q[i[0], i[1], i[2], i[3]].double() - k[i[0], :, i[2], i[3]].double())
+        return scale * float((sg * g[i[0], :, i[1], i[2]].double()).sum())
+
+    def dk_at(i):  # (b, s, h, w)
+        sg = torch.sign(q[i[0], :, i[2], i[3]].double() - k[i[0], i[1], i[2], i[3]].double())
+        return -scale * float((sg * g[i[0], i[1], :, i[2]].double()).sum())
+
+    _agree_or_reference_race(ours[0], theirs[0], dq_at, 1e-5, "d_q", racy)
+    _agree_or_reference_race(ours[1], theirs[1], dk_at, 1e-5, "d_k", racy)
 
 
 @pytest.mark.parametrize("qk_scale", [1.0, 0.25])
