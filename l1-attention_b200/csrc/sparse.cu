@@ -357,10 +357,10 @@ __global__ void __launch_bounds__(256) sparse_fwd_src_kernel(SparseArgs a, const
 //   softmax: dx_r = a_r (ds_r - sum_j a_j ds_j)   [same as the reference's Jacobian product,
 //            cuda/l1attn_sparse_cuda_kernel.cu:256-295, without its O(dst_mxlen^2) loop]
 //   else:    dx_r = a_r ds_r
-// (three CTAs per SM: the kernel waits on gathered rows most of the time, and 24 resident warps with a few
-// spilled values measured 4 % faster than 16 warps with none)
-template <typename T, int VEC, int LPHC, int NX>
-__global__ void __launch_bounds__(256, 3) sparse_bwd_dst_kernel(SparseArgs a, const T *__restrict__ dvo,
+// For the common widths ONE walk over the slots does all of it (see the NX > 0 branch): 121 registers, two CTAs
+// per SM.  The generic branch walks the list once per quantity and is capped at three CTAs per SM.
+template <typename T, int VEC, int LPHC, int NX, bool BIDI>
+__global__ void __launch_bounds__(256, NX == 4 ? 2 : 3) sparse_bwd_dst_kernel(SparseArgs a, const T *__restrict__ dvo,
 							      const T *__restrict__ v, const T *__restrict__ vb,
 							      const T *__restrict__ q, const T *__restrict__ k,
 							      const T *__restrict__ attn, T *dx, T *__restrict__ d_q,
@@ -381,6 +381,103 @@ __global__ void __launch_bounds__(256, 3) sparse_bwd_dst_kernel(SparseArgs a, co
 	const T *gdst = dvo + ((tokrow + dst) * H + hh) * Wv;
 	const T *bdst = a.bidi ? vb + ((tokrow + dst) * H + hh) * Wv : nullptr;
 
+	if constexpr (NX > 0) {
+		// One walk over the slots: v[src] and k[src] (and dvo[src] when bidirectional) of a slot are gathered
+		// together.  ds_r needs only this slot's rows, but dx_r = a_r (ds_r - S) needs S = sum_j a_j ds_j of the
+		// whole list, so d_q is accumulated in two parts and combined at the end:
+		//   d_q = scale * sum_r sgn_r dx_r = scale * (sum_r sgn_r a_r ds_r  -  S * sum_r sgn_r a_r),  sgn_r = sign(q - k[src_r]).
+		Pack<T, VEC> qv[NX], gd[NX], bd[NX], acc1[NX], acc2[NX], accb[NX];
+		const T *qrow = q + ((tokrow + dst) * H + hh) * W + w.li * VEC;
+#pragma unroll
+		for (int it = 0; it < NX; it++) {
+			qv[it] = ldv<T, VEC>(qrow + it * step, w.head_ok);
+			gd[it] = ldv<T, VEC>(gdst + w.li * VEC + it * step, true);
+			bd[it] = ldv<T, VEC>(BIDI ? bdst + w.li * VEC + it * step : gdst, BIDI);
+		}
+		zero_acc(acc1);
+		zero_acc(acc2);
+		zero_acc(accb);
+		const T *vbase = v + (tokrow * H + hh) * Wv + w.li * VEC, *kbase = k + (tokrow * H + hh) * W + w.li * VEC;
+		const T *gbase = dvo + (tokrow * H + hh) * Wv + w.li * VEC;
+		T S = T(0);
+		for (int r = 0; r < dm; r++) {
+			const int src = slots[r];
+			const bool ok = w.head_ok && src >= 0;
+			const size_t so = size_t(ok ? src : 0) * H;
+			Pack<T, VEC> vr[NX], kr[NX], gr[NX];
+#pragma unroll
+			for (int it = 0; it < NX; it++) {
+				vr[it] = ldv<T, VEC>(vbase + so * Wv + it * step, true);
+				kr[it] = ldv<T, VEC>(kbase + so * W + it * step, true);
+			}
+			if (BIDI) {
+#pragma unroll
+				for (int it = 0; it < NX; it++)
+					gr[it] = ldv<T, VEC>(gbase + so * Wv + it * step, true);
+			}
+			const T ar = ok ? arow[size_t(r) * H] : T(0);
+			T part = T(0);
+#pragma unroll
+			for (int it = 0; it < NX; it++)
+#pragma unroll
+				for (int i = 0; i < VEC; i++)
+					part += vr[it].v[i] * gd[it].v[i];
+			if (BIDI) {
+#pragma unroll
+				for (int it = 0; it < NX; it++)
+#pragma unroll
+					for (int i = 0; i < VEC; i++)
+						part += bd[it].v[i] * gr[it].v[i];
+			}
+			part = group_sum<LPHC>(part, lph);
+			if (!ok)
+				continue; // (uniform over the lanes of a head; the shuffles above ran for the whole warp)
+			S += ar * part;
+			if (w.li == 0)
+				xrow[size_t(r) * H] = part;
+			const T w1 = ar * part;
+#pragma unroll
+			for (int it = 0; it < NX; it++)
+#pragma unroll
+				for (int i = 0; i < VEC; i++) {
+					const T sg = sign_apply(qv[it].v[i] - kr[it].v[i], T(1));
+					acc1[it].v[i] += sg * w1;
+					acc2[it].v[i] += sg * ar;
+				}
+			if (BIDI) {
+#pragma unroll
+				for (int it = 0; it < NX; it++)
+#pragma unroll
+					for (int i = 0; i < VEC; i++)
+						accb[it].v[i] += ar * gr[it].v[i];
+			}
+		}
+		__syncwarp();
+		if (w.head_ok) {
+			for (int r = w.li; r < dm; r += lph) { // ds -> dx for the src pass
+				if (slots[r] < 0)
+					continue;
+				const T ar = arow[size_t(r) * H], ds = xrow[size_t(r) * H];
+				xrow[size_t(r) * H] = a.use_softmax ? ar * (ds - S) : ar * ds;
+			}
+			T *orow = d_q + ((tokrow + dst) * H + hh) * W + w.li * VEC;
+			const T sfac = a.use_softmax ? S : T(0);
+#pragma unroll
+			for (int it = 0; it < NX; it++) {
+#pragma unroll
+				for (int i = 0; i < VEC; i++)
+					acc1[it].v[i] = (acc1[it].v[i] - sfac * acc2[it].v[i]) * scale;
+				*reinterpret_cast<Pack<T, VEC> *>(orow + it * step) = acc1[it];
+			}
+			if (BIDI) { // d_vb[dst] = sum_r a_r dvo[src_r]
+				T *brow = d_vb + ((tokrow + dst) * H + hh) * Wv + w.li * VEC;
+#pragma unroll
+				for (int it = 0; it < NX; it++)
+					*reinterpret_cast<Pack<T, VEC> *>(brow + it * step) = accb[it];
+			}
+		}
+		return;
+	}
 	T S = T(0);
 	for (int r0 = 0; r0 < dm; r0 += U) {
 		int src[U];
@@ -439,50 +536,6 @@ __global__ void __launch_bounds__(256, 3) sparse_bwd_dst_kernel(SparseArgs a, co
 
 	const T *qrow = q + ((tokrow + dst) * H + hh) * W;
 	T *orow = d_q + ((tokrow + dst) * H + hh) * W;
-	if constexpr (NX > 0) {
-		Pack<T, VEC> acc[NX], qv[NX];
-		zero_acc(acc);
-#pragma unroll
-		for (int it = 0; it < NX; it++)
-			qv[it] = ldv<T, VEC>(qrow + w.li * VEC + it * step, w.head_ok);
-		const T *kbase = k + (tokrow * H + hh) * W + w.li * VEC;
-		walk_list<T, T, VEC, NX, 1>(acc, qv, dm, step, [&](int r, const T *&ptr, T &wgt) {
-			const int src = slots[r];
-			const bool ok = w.head_ok && src >= 0;
-			ptr = kbase + size_t(ok ? src : 0) * H * W;
-			if (ok)
-				wgt = xrow[size_t(r) * H];
-			return ok;
-		});
-		if (w.head_ok) {
-#pragma unroll
-			for (int it = 0; it < NX; it++) {
-#pragma unroll
-				for (int i = 0; i < VEC; i++)
-					acc[it].v[i] *= scale;
-				*reinterpret_cast<Pack<T, VEC> *>(orow + w.li * VEC + it * step) = acc[it];
-			}
-		}
-		if (a.bidi) { // d_vb[dst] = sum_r a_r dvo[src_r]
-			T *brow = d_vb + ((tokrow + dst) * H + hh) * Wv;
-			zero_acc(acc);
-			const T *gbase = dvo + (tokrow * H + hh) * Wv + w.li * VEC;
-			walk_list<T, T, VEC, NX, 0>(acc, acc, dm, step, [&](int r, const T *&ptr, T &wgt) {
-				const int src = slots[r];
-				const bool ok = w.head_ok && src >= 0;
-				ptr = gbase + size_t(ok ? src : 0) * H * Wv;
-				if (ok)
-					wgt = arow[size_t(r) * H];
-				return ok;
-			});
-			if (w.head_ok) {
-#pragma unroll
-				for (int it = 0; it < NX; it++)
-					*reinterpret_cast<Pack<T, VEC> *>(brow + w.li * VEC + it * step) = acc[it];
-			}
-		}
-		return;
-	}
 	L1B_XLOOP(W) {
 		const Pack<T, VEC> qv = ldv<T, VEC>(qrow + x, w.head_ok);
 		Pack<T, VEC> acc = ldv<T, VEC>(nullptr, false);
@@ -555,38 +608,42 @@ __global__ void __launch_bounds__(256) sparse_bwd_src_kernel(SparseArgs a, const
 	const int step = lph * VEC;
 	T *vrow = d_v + ((tokrow + src) * H + w.h) * Wv;
 	if constexpr (NX > 0) {
-		Pack<T, VEC> acc[NX], kv[NX];
-		zero_acc(acc);
-		const T *gbase = dvo + (tokrow * H + w.h) * Wv + w.li * VEC;
+		// one walk over the incoming edges: dvo[dst] and q[dst] of an edge are gathered together
+		Pack<T, VEC> accv[NX], acck[NX], kv[NX];
+		zero_acc(accv);
+		zero_acc(acck);
+		const T *krow = k + ((tokrow + src) * H + w.h) * W + w.li * VEC;
+#pragma unroll
+		for (int it = 0; it < NX; it++)
+			kv[it] = ldv<T, VEC>(krow + it * step, true);
+		const T *gbase = dvo + (tokrow * H + w.h) * Wv + w.li * VEC, *qbase = q + (tokrow * H + w.h) * W + w.li * VEC;
 		const T *abase = attn + (tokrow * dm) * H + w.h, *xbase = dx + (tokrow * dm) * H + w.h;
-		walk_list<T, T, VEC, NX, 0>(acc, acc, e1 - e0, step, [&](int e, const T *&ptr, T &wgt) {
-			const int slot = a.csc_slot[e0 + e];
-			ptr = gbase + size_t(slot / dm) * H * Wv;
-			wgt = abase[size_t(slot) * H];
-			return true;
-		});
+		for (int e = e0; e < e1; e++) {
+			const int slot = a.csc_slot[e];
+			const size_t d = size_t(slot / dm) * H;
+			Pack<T, VEC> gr[NX], qr[NX];
 #pragma unroll
-		for (int it = 0; it < NX; it++)
-			*reinterpret_cast<Pack<T, VEC> *>(vrow + w.li * VEC + it * step) = acc[it];
-		const T *krow = k + ((tokrow + src) * H + w.h) * W;
-		T *orow = d_k + ((tokrow + src) * H + w.h) * W;
+			for (int it = 0; it < NX; it++) {
+				gr[it] = ldv<T, VEC>(gbase + d * Wv + it * step, true);
+				qr[it] = ldv<T, VEC>(qbase + d * W + it * step, true);
+			}
+			const T ar = abase[size_t(slot) * H], dxr = xbase[size_t(slot) * H];
 #pragma unroll
-		for (int it = 0; it < NX; it++)
-			kv[it] = ldv<T, VEC>(krow + w.li * VEC + it * step, true);
-		zero_acc(acc);
-		const T *qbase = q + (tokrow * H + w.h) * W + w.li * VEC;
-		walk_list<T, T, VEC, NX, 2>(acc, kv, e1 - e0, step, [&](int e, const T *&ptr, T &wgt) {
-			const int slot = a.csc_slot[e0 + e];
-			ptr = qbase + size_t(slot / dm) * H * W;
-			wgt = xbase[size_t(slot) * H];
-			return true;
-		});
+			for (int it = 0; it < NX; it++)
+#pragma unroll
+				for (int i = 0; i < VEC; i++) {
+					accv[it].v[i] += ar * gr[it].v[i];
+					acck[it].v[i] += sign_apply(qr[it].v[i] - kv[it].v[i], dxr);
+				}
+		}
+		T *orow = d_k + ((tokrow + src) * H + w.h) * W + w.li * VEC;
 #pragma unroll
 		for (int it = 0; it < NX; it++) {
+			*reinterpret_cast<Pack<T, VEC> *>(vrow + w.li * VEC + it * step) = accv[it];
 #pragma unroll
 			for (int i = 0; i < VEC; i++)
-				acc[it].v[i] *= -scale;
-			*reinterpret_cast<Pack<T, VEC> *>(orow + w.li * VEC + it * step) = acc[it];
+				acck[it].v[i] *= -scale;
+			*reinterpret_cast<Pack<T, VEC> *>(orow + it * step) = acck[it];
 		}
 		return;
 	}
@@ -709,7 +766,9 @@ int bwd_t(SparseArgs a, const T *dvo, const T *v, const T *vb, const T *q, const
 	  T *d_vb, T *d_q, T *d_k, T *dx, cudaStream_t st)
 {
 	const int mw = a.width > a.v_width ? a.width : a.v_width;
-	a.lph = pow2_ceil((mw + 4 * VEC - 1) / (4 * VEC)); // four 16-byte vectors per lane: fewer shuffle rounds and less index math per term
+	// four 16-byte vectors per lane: fewer shuffle rounds and less index math per term (two per lane, twice the
+	// warps at ~75 registers, measured 2 % slower)
+	a.lph = pow2_ceil((mw + 4 * VEC - 1) / (4 * VEC));
 	if (a.lph > 32)
 		a.lph = 32;
 	const Grid g = grid_for(a);
@@ -718,7 +777,10 @@ int bwd_t(SparseArgs a, const T *dvo, const T *v, const T *vb, const T *q, const
 	const T scale = T(-1.0 / sqrt(double(a.width)));
 #define L1B_BWD(LP, NXV)                                                                                                       \
 	do {                                                                                                              \
-		sparse_bwd_dst_kernel<T, VEC, LP, NXV><<<g.blocks, 256, 0, st>>>(a, dvo, v, vb, q, k, attn, dx, d_q, d_vb, scale); \
+		if (a.bidi)                                                                                               \
+			sparse_bwd_dst_kernel<T, VEC, LP, NXV, true><<<g.blocks, 256, 0, st>>>(a, dvo, v, vb, q, k, attn, dx, d_q, d_vb, scale); \
+		else                                                                                                      \
+			sparse_bwd_dst_kernel<T, VEC, LP, NXV, false><<<g.blocks, 256, 0, st>>>(a, dvo, v, vb, q, k, attn, dx, d_q, d_vb, scale); \
 		L1B_LAUNCH_CHECK();                                                                                       \
 		sparse_bwd_src_kernel<T, VEC, LP, NXV><<<g.blocks, 256, 0, st>>>(a, dvo, q, k, attn, dx, d_v, d_k, scale);        \
 		L1B_LAUNCH_CHECK();                                                                                       \
