@@ -646,7 +646,7 @@ def roofline_of(wl, t, pk, clocks, l2_gbs=None):
 DENSE_LAUNCHES_PER_STEP = 4
 # ncu dram__bytes_read.sum + dram__bytes_write.sum per launch at the profiling sizes (profiles/*.md)
 DENSE_BWD_TRAFFIC_B2 = 314.9e6
-SPARSE_TRAFFIC_B2 = 230.7e6
+SPARSE_TRAFFIC_B2 = 226.9e6
 
 
 def module_step_ms(torch, wl, steps):

@@ -68,6 +68,20 @@ int l1attn_last_cuda_error(void);
  * tiles with asynchronous bulk copies never spin without a limit.  L1ATTN_OK otherwise.
  */
 int l1attn_device_status(void);
+/*
+ * The same word without a synchronisation: enqueues a copy of it to *host_word on `stream` (use pinned host
+ * memory) and returns; the word is not cleared.  A caller that launches on one stream can thus look at
+ * *host_word before its next call and pay for l1attn_device_status() only when it is non-zero.
+ * No counterpart in the reference, whose kernels have no waits and whose launchers check no errors.
+ */
+int l1attn_device_status_async(int *host_word, void *stream);
+/*
+ * Test hook, not an operator: launches one warp that waits at most limit_us (1..100000) microseconds on a
+ * barrier nothing completes.  The wait gives up, l1attn_device_status() then reports L1ATTN_ERR_TIMEOUT once
+ * and L1ATTN_OK after; *returned_dev (device int) is set to 1 when the kernel has returned from the wait.
+ * Nothing faults or hangs.  No counterpart in the reference.
+ */
+int l1attn_test_wait_timeout(int limit_us, int *returned_dev, void *stream);
 
 /* ------------------------------------------------------------------ dense --------------- */
 

@@ -47,7 +47,9 @@ __global__ void __launch_bounds__(32) rank_by_key_kernel(const K *keys, int stri
 		int rank = -1;
 		if (valid) {
 			const unsigned m = __match_any_sync(act, key);
-			rank = cnt[key] + __popc(m & ((1u << lane) - 1u));
+			const int seen = cnt[key]; // every lane of the group reads the counter ...
+			__syncwarp(act);           // ... before its highest lane overwrites it
+			rank = seen + __popc(m & ((1u << lane) - 1u));
 			if (lane == 31 - __clz(m))
 				cnt[key] = rank + 1;
 		}

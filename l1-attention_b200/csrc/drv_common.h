@@ -49,3 +49,40 @@ inline void l1b_status(int rc, const char *fn)
 }
 
 inline void *l1b_stream() { return static_cast<void *>(at::cuda::getCurrentCUDAStream().stream()); }
+
+// A kernel of the library that gives up a bounded wait sets a sticky word on the device and returns; its outputs
+// are then garbage.  The drivers never synchronise, so they learn of it one call late: after every launch the
+// word is copied, on the same stream, to a pinned host word (l1b_poll_status); the next driver call looks at that
+// word first (l1b_check_pending) and raises if it is set.  A caller that needs the answer at once can call
+// l1attn_device_status() through the C ABI, which synchronises.
+inline int *l1b_status_word()
+{
+	static int *word = [] {
+		int *p = nullptr;
+		if (cudaHostAlloc(reinterpret_cast<void **>(&p), 64, cudaHostAllocDefault) != cudaSuccess) {
+			(void)cudaGetLastError();
+			return static_cast<int *>(nullptr);
+		}
+		*p = 0;
+		return p;
+	}();
+	return word;
+}
+
+inline void l1b_check_pending(const char *fn)
+{
+	int *w = l1b_status_word();
+	if (w && *reinterpret_cast<volatile int *>(w) != 0) {
+		*w = 0;
+		(void)l1attn_device_status(); // synchronises and clears the device word
+		TORCH_CHECK(false, fn, ": an earlier kernel of this library gave up a bounded wait on an asynchronous copy; "
+				       "the results of the calls made since the previous successful call are invalid");
+	}
+}
+
+inline void l1b_poll_status()
+{
+	int *w = l1b_status_word();
+	if (w)
+		(void)l1attn_device_status_async(w, l1b_stream());
+}

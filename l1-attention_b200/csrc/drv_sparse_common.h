@@ -4,8 +4,12 @@
 // want an edge index derived from coo (slot table + per-source lists); it is built on first use
 // and cached per coo tensor, keyed on (storage pointer, version counter, sizes), so a graph that
 // is reused across layers and steps is indexed once.  The cache keeps the coo tensor alive, so a
-// freed-and-reused pointer cannot alias a stale entry.
+// freed-and-reused pointer cannot alias a stale entry.  A write that bypasses the version counter
+// (coo.data[...] = ..., a raw-pointer kernel) is NOT seen: do not edit coo in place that way, or call
+// clear_index_cache() (bound in both sparse modules) afterwards.  The cache holds at most 16 graphs.
 #pragma once
+#include <climits>
+#include <cstdint>
 #include <list>
 #include <mutex>
 #include "drv_common.h"
@@ -16,12 +20,30 @@ struct L1bIndexEntry {
 	int n_tok, dst_mxlen;
 };
 
+struct L1bIndexCache {
+	std::mutex mu;
+	std::list<L1bIndexEntry> entries; // most recent first
+};
+inline L1bIndexCache &l1b_index_cache()
+{
+	static L1bIndexCache c;
+	return c;
+}
+
+// Drops every cached edge index (and the coo tensors they keep alive).
+inline void l1b_clear_index_cache()
+{
+	L1bIndexCache &c = l1b_index_cache();
+	std::lock_guard<std::mutex> lock(c.mu);
+	c.entries.clear();
+}
+
 inline torch::Tensor l1b_index_for(const torch::Tensor &coo, int n_tok, int dst_mxlen)
 {
-	static std::mutex mu;
-	static std::list<L1bIndexEntry> cache; // most recent first
+	L1bIndexCache &holder = l1b_index_cache();
+	std::list<L1bIndexEntry> &cache = holder.entries;
 	const size_t max_entries = 16;
-	std::lock_guard<std::mutex> lock(mu);
+	std::lock_guard<std::mutex> lock(holder.mu);
 	const uint32_t ver = coo._version();
 	for (auto it = cache.begin(); it != cache.end(); ++it) {
 		if (it->coo.data_ptr() == coo.data_ptr() && it->version == ver && it->coo.sizes() == coo.sizes() &&
@@ -140,7 +162,10 @@ inline std::tuple<torch::Tensor, int, int> l1b_expand_coo(torch::Tensor co)
 			   "l1attn_i64_minmax");
 		auto mmh = mm.cpu();
 		lo = mmh[0].item<int64_t>();
-		nkeys = mmh[1].item<int64_t>() - lo + 1;
+		const long long hi = mmh[1].item<int64_t>();
+		// the expanded list is int32 (as the reference's is); the rank counters take memory proportional to hi - lo
+		TORCH_CHECK(lo >= INT32_MIN && hi <= INT32_MAX, "expandCoo: token ids must fit in int32, got [", lo, ", ", hi, "]");
+		nkeys = hi - lo + 1;
 		const size_t nb = l1attn_expand_coo_scratch_bytes(nkeys);
 		if (nb) {
 			counters = torch::empty({(long)(nb / 4)}, i32);

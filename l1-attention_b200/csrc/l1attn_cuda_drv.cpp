@@ -8,6 +8,7 @@
 
 std::vector<torch::Tensor> l1attn_forward(torch::Tensor q, torch::Tensor k)
 {
+	l1b_check_pending("l1attn forward");
 	CHECK_INPUT(q);
 	CHECK_INPUT(k);
 	TORCH_CHECK(q.dim() == 4, "q must be [batch, n_tokens, heads, width]");
@@ -18,11 +19,13 @@ std::vector<torch::Tensor> l1attn_forward(torch::Tensor q, torch::Tensor k)
 	auto attn = torch::empty({bs, n, n, h}, q.options().requires_grad(false));
 	l1b_status(l1attn_dense_fwd(q.data_ptr(), k.data_ptr(), attn.data_ptr(), bs, n, h, w, dt, l1b_stream()),
 		   "l1attn_dense_fwd");
+	l1b_poll_status();
 	return {attn};
 }
 
 std::vector<torch::Tensor> l1attn_backward(torch::Tensor d_attn, torch::Tensor q, torch::Tensor k)
 {
+	l1b_check_pending("l1attn backward");
 	CHECK_INPUT(d_attn);
 	CHECK_INPUT(q);
 	CHECK_INPUT(k);
@@ -41,6 +44,7 @@ std::vector<torch::Tensor> l1attn_backward(torch::Tensor d_attn, torch::Tensor q
 	l1b_status(l1attn_dense_bwd(d_attn.data_ptr(), q.data_ptr(), k.data_ptr(), d_q.data_ptr(), d_k.data_ptr(),
 				    scratch.data_ptr(), bs, n, h, w, dt, l1b_stream()),
 		   "l1attn_dense_bwd");
+	l1b_poll_status();
 	return {d_q, d_k};
 }
 

@@ -34,4 +34,5 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m)
 	m.def("forward", &l1attnSparseBidi_forward, "L1AttnSparseBidi forward (CUDA, sm_100a)");
 	m.def("backward", &l1attnSparseBidi_backward, "L1AttnSparseBidi backward (CUDA, sm_100a)");
 	m.def("expand_coo", &l1b_expand_coo, "expandCoo on the GPU");
+	m.def("clear_index_cache", &l1b_clear_index_cache, "drop the cached edge indexes of this module");
 }

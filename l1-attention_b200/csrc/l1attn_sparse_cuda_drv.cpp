@@ -31,4 +31,5 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m)
 	m.def("forward", &l1attnSparse_forward, "L1AttnSparse forward (CUDA, sm_100a)");
 	m.def("backward", &l1attnSparse_backward, "L1AttnSparse backward (CUDA, sm_100a)");
 	m.def("expand_coo", &l1b_expand_coo, "expandCoo on the GPU");
+	m.def("clear_index_cache", &l1b_clear_index_cache, "drop the cached edge indexes of this module");
 }

@@ -72,3 +72,47 @@ extern "C" int l1attn_device_status(void)
 	}
 	return L1ATTN_OK;
 }
+
+// Copies the error word to *host_word on `stream` without waiting and without clearing it.  With host_word in
+// pinned memory a caller can look at the word before its next launch and call l1attn_device_status() only when
+// it is set.
+extern "C" int l1attn_device_status_async(int *host_word, void *stream)
+{
+	int *p = l1b::device_error_word();
+	if (!p || !host_word)
+		return L1ATTN_ERR_ARG;
+	L1B_CUDA(cudaMemcpyAsync(host_word, p, sizeof(int), cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream)));
+	return L1ATTN_OK;
+}
+
+namespace l1b {
+namespace {
+// One warp waits on a barrier that nothing ever completes, with a short limit: the wait runs out, the error word
+// is set and the kernel returns.  Nothing faults and nothing hangs; it exists so that the give-up path of
+// mbar_wait and the error word's set / read / clear cycle can be exercised.
+__global__ void wait_timeout_probe_kernel(unsigned long long limit_ns, int *err, int *returned)
+{
+	__shared__ __align__(8) uint64_t bar;
+	if (threadIdx.x == 0) {
+		mbar_init(&bar, 1);
+		mbar_fence_init();
+	}
+	__syncthreads();
+	const bool ok = mbar_wait(&bar, 0, err, limit_ns);
+	if (threadIdx.x == 0)
+		*returned = ok ? 2 : 1;
+}
+} // namespace
+} // namespace l1b
+
+extern "C" int l1attn_test_wait_timeout(int limit_us, int *returned_dev, void *stream)
+{
+	if (limit_us < 1 || limit_us > 100000 || !returned_dev)
+		return L1ATTN_ERR_ARG;
+	int *err = l1b::device_error_word();
+	if (!err)
+		return L1ATTN_ERR_CUDA;
+	l1b::wait_timeout_probe_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(1000ull * limit_us, err, returned_dev);
+	L1B_LAUNCH_CHECK();
+	return L1ATTN_OK;
+}

@@ -5,8 +5,9 @@
 //  * the innermost coordinate of every copy is a multiple of 16 bytes (callers pass width
 //    offsets that are multiples of the 64-byte stage row, and 0 for the head/row axes that are
 //    innermost in their tensors);
-//  * every wait is bounded: after WAIT_LIMIT failed polls the waiter records an error code in
-//    the device error word and gives up, so a lost copy can never hang the GPU.
+//  * every wait is bounded in TIME: a waiter that has polled without success for WAIT_LIMIT_NS (by the
+//    global nanosecond timer, read every 64 failed polls) records an error code in the device error
+//    word and gives up, so a lost copy cannot hang the GPU.
 #pragma once
 #include <cuda.h>
 #include <cuda_runtime.h>
@@ -18,7 +19,14 @@ namespace l1b {
 // wait ran out stores a non-zero code there.  Read and cleared by l1attn_device_status().
 int *device_error_word();
 
-constexpr uint32_t WAIT_LIMIT = 1u << 24; // polls; each try_wait itself blocks for a hardware time slice
+constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull; // two seconds: orders of magnitude beyond any copy these kernels wait for
+
+__device__ __forceinline__ uint64_t global_timer_ns()
+{
+	uint64_t t;
+	asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+	return t;
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 
@@ -38,11 +46,14 @@ __device__ __forceinline__ void mbar_arrive(uint64_t *bar)
 {
 	asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
-// true when the phase with the given parity has completed; false after WAIT_LIMIT polls
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, int *err)
+// true when the phase with the given parity has completed; false once limit_ns have passed without that
+// (the timer is only read on the slow path: every 64th failed poll, each of which already suspends the thread
+// for a hardware time slice)
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, int *err, uint64_t limit_ns = WAIT_LIMIT_NS)
 {
 	const uint32_t a = smem_u32(bar);
-	for (uint32_t i = 0; i < WAIT_LIMIT; i++) {
+	uint64_t t0 = 0;
+	for (uint32_t i = 1;; i++) {
 		uint32_t ok;
 		asm volatile("{\n\t.reg .pred p;\n\t"
 			     "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
@@ -52,6 +63,13 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, int *e
 			     : "memory");
 		if (ok)
 			return true;
+		if ((i & 63u) == 0u) {
+			const uint64_t now = global_timer_ns();
+			if (t0 == 0)
+				t0 = now;
+			else if (now - t0 > limit_ns)
+				break;
+		}
 	}
 	*err = 1;
 	return false;

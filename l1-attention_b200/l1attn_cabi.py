@@ -25,6 +25,8 @@ SIGNATURES = {
     "l1attn_strerror": (_c.c_char_p, [_i]),
     "l1attn_last_cuda_error": (_i, []),
     "l1attn_device_status": (_i, []),
+    "l1attn_device_status_async": (_i, [_vp, _vp]),
+    "l1attn_test_wait_timeout": (_i, [_i, _vp, _vp]),
     "l1attn_dense_fwd": (_i, [_vp] * 3 + [_i] * 5 + [_vp]),
     "l1attn_dense_softmax_v_fwd": (_i, [_vp] * 5 + [_i] * 7 + [_vp]),
     "l1attn_dense_softmax_v_bwd_dx": (_i, [_vp] * 8 + [_i] * 6 + [_vp]),

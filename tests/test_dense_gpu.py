@@ -282,3 +282,52 @@ def test_pointers_aligned_to_the_element_only():
         assert_close(a.cpu().numpy(), b.cpu().numpy(), 1e-6, "sparse gradients")
     torch.cuda.synchronize()
     assert cabi.lib().l1attn_device_status() == 0
+
+
+def test_bounded_wait_gives_up_and_is_reported():
+    """Every wait of the TMA kernels is bounded in time.  Here one warp waits (limit 3 ms) on a barrier that nothing
+    completes: the wait gives up, the kernel returns, l1attn_device_status() reports the timeout exactly once, and
+    the library keeps working.  Nothing faults and nothing hangs -- a wait that runs out is the whole test."""
+    import time
+    cabi = _cabi()
+    lib = cabi.lib()
+    torch.cuda.synchronize()
+    assert lib.l1attn_device_status() == 0
+    returned = torch.zeros(1, dtype=torch.int32, device="cuda")
+    pinned = torch.zeros(16, dtype=torch.int32).pin_memory()
+    t0 = time.time()
+    assert lib.l1attn_test_wait_timeout(3000, returned.data_ptr(), None) == 0
+    assert lib.l1attn_device_status_async(pinned.data_ptr(), None) == 0  # the no-sync way to learn of it
+    torch.cuda.synchronize()
+    assert time.time() - t0 < 30.0
+    assert int(returned.item()) == 1, "the kernel must come back from the wait with `false`"
+    assert int(pinned[0]) == 1
+    assert lib.l1attn_device_status() == -7 and b"bounded wait" in lib.l1attn_strerror(-7)
+    assert lib.l1attn_device_status() == 0  # cleared by the read
+    assert lib.l1attn_test_wait_timeout(0, returned.data_ptr(), None) == -1  # limits outside 1 us .. 100 ms are refused
+    q, k, g = (torch.from_numpy(a).cuda() for a in _rand((1, 64, 8, 64), np.float32, 2))
+    a1 = cabi.dense_fwd(q, k)
+    torch.cuda.synchronize()
+    assert lib.l1attn_device_status() == 0 and torch.isfinite(a1).all()
+
+
+def test_driver_raises_on_a_pending_timeout():
+    """The pybind driver never synchronises; it polls the error word through pinned memory and raises at the next
+    call after a kernel gave up a wait."""
+    import l1attn_cuda_drv
+    cabi = _cabi()
+    lib = cabi.lib()
+    q = torch.randn(1, 32, 8, 64, device="cuda")
+    l1attn_cuda_drv.forward(q, q)
+    torch.cuda.synchronize()
+    l1attn_cuda_drv.forward(q, q)  # nothing pending: fine
+    returned = torch.zeros(1, dtype=torch.int32, device="cuda")
+    assert lib.l1attn_test_wait_timeout(2000, returned.data_ptr(), torch.cuda.current_stream().cuda_stream) == 0
+    l1attn_cuda_drv.forward(q, q)  # enqueued behind the probe; copies the (now set) word to the pinned word
+    torch.cuda.synchronize()
+    with pytest.raises(RuntimeError, match="bounded wait"):
+        l1attn_cuda_drv.forward(q, q)
+    assert lib.l1attn_device_status() == 0  # the raise cleared it
+    out = l1attn_cuda_drv.forward(q, q)[0]
+    torch.cuda.synchronize()
+    assert torch.isfinite(out).all()

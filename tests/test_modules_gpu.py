@@ -188,6 +188,31 @@ def test_index_cache_sees_in_place_edits():
     assert not torch.equal(a[0, 0], b[0, 0])
 
 
+def test_index_cache_can_be_cleared():
+    """A write that does not bump the tensor's version counter is invisible to the cache; clear_index_cache()
+    is the documented way out."""
+    import l1attn_sparse_cuda_drv as drv
+    q = torch.randn(1, 4, 1, 8, device="cuda")
+    coo = torch.tensor([[0, 1, 0, 0], [2, 3, 0, 0]], dtype=torch.int32, device="cuda")
+    a, _ = drv.forward(q, q, q, coo, 1, False)
+    coo.data[0, 1] = 2  # behind autograd's back: same version
+    drv.clear_index_cache()
+    b, _ = drv.forward(q, q, q, coo, 1, False)
+    assert not torch.equal(a[0, 0], b[0, 0])
+
+
+def test_expandcoo_rejects_ids_beyond_int32():
+    import l1attn_sparse_cuda
+    with pytest.raises(RuntimeError, match="int32"):
+        l1attn_sparse_cuda.expandCoo(torch.tensor([[0, 1], [1 << 40, 2]]))
+    import l1attn_cabi
+    import ctypes
+    co = np.array([[0, 1], [1 << 40, 2]], dtype=np.int64)
+    coo = np.zeros((2, 4), dtype=np.int32)
+    dm, sm = ctypes.c_int(0), ctypes.c_int(0)
+    assert l1attn_cabi.lib().l1attn_expand_coo_host(co.ctypes.data, 2, coo.ctypes.data, ctypes.byref(dm), ctypes.byref(sm)) == -2
+
+
 def _ref_cuda(name):
     import importlib
     import os

@@ -49,11 +49,25 @@ def test_static_scratch_backward_matches_regular_entry_point():
         # outputs pre-allocated, so the call under test performs no allocation of any kind
         out = (torch.empty_like(t["v"]), torch.empty_like(t["v"]) if bidi else None,
                torch.empty_like(t["q"]), torch.empty_like(t["k"]))
-        n_alloc = torch.cuda.memory_stats()["allocation.all.allocated"]  # cumulative count of torch allocations
-        got = cabi.sparse_bwd_static(t["dvo"], t["v"], t["q"], t["k"], index, attn, True, vb=t["vb"], out=out)
-        assert torch.cuda.memory_stats()["allocation.all.allocated"] == n_alloc
         torch.cuda.synchronize()
+        n_alloc = torch.cuda.memory_stats()["allocation.all.allocated"]  # cumulative count of torch allocations
+        free_before, _ = torch.cuda.mem_get_info()                         # cudaMemGetInfo: sees the runtime's own allocations too
+        got = cabi.sparse_bwd_static(t["dvo"], t["v"], t["q"], t["k"], index, attn, True, vb=t["vb"], out=out)
+        torch.cuda.synchronize()
+        free_after, _ = torch.cuda.mem_get_info()
+        assert torch.cuda.memory_stats()["allocation.all.allocated"] == n_alloc
+        if seed > 0:  # (the very first call on a device may load the kernels' module image, which the driver places in device memory)
+            assert free_after == free_before, "device memory in use changed across the call: %d -> %d" % (free_before, free_after)
         assert lib.l1attn_device_status() == 0
+        # ... and against the CPU oracle, like the other sparse tests (fp32: 1e-5 norm-wise)
+        from oracle import oracle
+        f64 = lambda x: None if x is None else x.cpu().double().numpy()
+        if bidi:
+            ref = oracle.sparse_bidi_bwd(f64(t["dvo"]), f64(t["v"]), f64(t["vb"]), f64(t["q"]), f64(t["k"]), coo_h, f64(attn), dm, True)
+        else:
+            ref = oracle.sparse_bwd(f64(t["dvo"]), f64(t["v"]), f64(t["q"]), f64(t["k"]), coo_h, f64(attn), dm, True)
+        for a, r in zip(got, ref):
+            assert_close(a.cpu().numpy(), r, 1e-5, "static-scratch backward vs oracle")
         for a, b in zip(got, want):
             # same kernels, same order of operations: equal to the last bit, and so within the
             # 1e-5 fp32 tolerance of the other sparse tests
