@@ -78,7 +78,8 @@ int l1attn_device_status_async(int *host_word, void *stream);
 /*
  * Test hook, not an operator: launches one warp that waits at most limit_us (1..100000) microseconds on a
  * barrier nothing completes.  The wait gives up, l1attn_device_status() then reports L1ATTN_ERR_TIMEOUT once
- * and L1ATTN_OK after; *returned_dev (device int) is set to 1 when the kernel has returned from the wait.
+ * and L1ATTN_OK after; returned_dev (two device ints) receives {1, number of failed polls} when the kernel
+ * has returned from the wait.
  * Nothing faults or hangs.  No counterpart in the reference.
  */
 int l1attn_test_wait_timeout(int limit_us, int *returned_dev, void *stream);

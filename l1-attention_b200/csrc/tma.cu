@@ -91,16 +91,19 @@ namespace {
 // is set and the kernel returns.  Nothing faults and nothing hangs; it exists so that the give-up path of
 // mbar_wait and the error word's set / read / clear cycle can be exercised.
 __global__ void wait_timeout_probe_kernel(unsigned long long limit_ns, int *err, int *returned)
-{
+{ // returned[0]: 1 = the wait gave up, 2 = it succeeded (cannot happen); returned[1]: failed polls of thread 0
 	__shared__ __align__(8) uint64_t bar;
 	if (threadIdx.x == 0) {
 		mbar_init(&bar, 1);
 		mbar_fence_init();
 	}
 	__syncthreads();
-	const bool ok = mbar_wait(&bar, 0, err, limit_ns);
-	if (threadIdx.x == 0)
-		*returned = ok ? 2 : 1;
+	unsigned polls = 0;
+	const bool ok = mbar_wait_timed(&bar, 0, err, limit_ns, &polls);
+	if (threadIdx.x == 0) {
+		returned[0] = ok ? 2 : 1;
+		returned[1] = int(polls);
+	}
 }
 } // namespace
 } // namespace l1b

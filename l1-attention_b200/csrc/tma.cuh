@@ -5,9 +5,9 @@
 //  * the innermost coordinate of every copy is a multiple of 16 bytes (callers pass width
 //    offsets that are multiples of the 64-byte stage row, and 0 for the head/row axes that are
 //    innermost in their tensors);
-//  * every wait is bounded in TIME: a waiter that has polled without success for WAIT_LIMIT_NS (by the
-//    global nanosecond timer, read every 64 failed polls) records an error code in the device error
-//    word and gives up, so a lost copy cannot hang the GPU.
+//  * every wait is bounded: after FAST_POLLS failed polls the waiter goes on by the global nanosecond
+//    timer for at most WAIT_LIMIT_NS, then records an error code in the device error word and gives
+//    up, so a lost copy cannot hang the GPU.
 #pragma once
 #include <cuda.h>
 #include <cuda_runtime.h>
@@ -46,33 +46,49 @@ __device__ __forceinline__ void mbar_arrive(uint64_t *bar)
 {
 	asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
-// true when the phase with the given parity has completed; false once limit_ns have passed without that
-// (the timer is only read on the slow path: every 64th failed poll, each of which already suspends the thread
-// for a hardware time slice)
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, int *err, uint64_t limit_ns = WAIT_LIMIT_NS)
+__device__ __forceinline__ bool mbar_try(uint32_t bar_addr, uint32_t parity)
+{
+	uint32_t ok;
+	asm volatile("{\n\t.reg .pred p;\n\t"
+		     "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+		     "selp.u32 %0, 1, 0, p;\n\t}"
+		     : "=r"(ok)
+		     : "r"(bar_addr), "r"(parity)
+		     : "memory");
+	return ok != 0;
+}
+
+// Waits by the clock alone: true when the phase with the given parity has completed, false (and *err set) once
+// limit_ns have passed without that.  *polls, when given, receives the number of failed polls.
+static __device__ __noinline__ bool mbar_wait_timed(uint64_t *bar, uint32_t parity, int *err, uint64_t limit_ns, unsigned *polls = nullptr)
 {
 	const uint32_t a = smem_u32(bar);
-	uint64_t t0 = 0;
-	for (uint32_t i = 1;; i++) {
-		uint32_t ok;
-		asm volatile("{\n\t.reg .pred p;\n\t"
-			     "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-			     "selp.u32 %0, 1, 0, p;\n\t}"
-			     : "=r"(ok)
-			     : "r"(a), "r"(parity)
-			     : "memory");
-		if (ok)
+	const uint64_t t0 = global_timer_ns();
+	unsigned n = 0;
+	bool ok = false;
+	while (!(ok = mbar_try(a, parity)) && global_timer_ns() - t0 <= limit_ns)
+		n++;
+	if (polls)
+		*polls = n;
+	if (!ok)
+		*err = 1;
+	return ok;
+}
+
+// The wait of the hot loops.  Its first phase is a bare poll loop and nothing else: waiting warps sit on the critical
+// path of a pipeline stage, and anything more in that loop (a clock read every n-th poll, a sleep, a suspend hint)
+// measured up to 1.8x slower kernels.  FAST_POLLS failed polls take about a second (each try_wait
+// suspends the thread for a hardware time slice, measured at 4 us by tests/test_dense_gpu.py); only then -- a copy is
+// late by orders of magnitude -- the wait goes on in a separate, clocked loop for at most WAIT_LIMIT_NS more
+// before it gives up.
+constexpr uint32_t FAST_POLLS = 1u << 18;
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, int *err)
+{
+	const uint32_t a = smem_u32(bar);
+	for (uint32_t i = 0; i < FAST_POLLS; i++)
+		if (mbar_try(a, parity))
 			return true;
-		if ((i & 63u) == 0u) {
-			const uint64_t now = global_timer_ns();
-			if (t0 == 0)
-				t0 = now;
-			else if (now - t0 > limit_ns)
-				break;
-		}
-	}
-	*err = 1;
-	return false;
+	return mbar_wait_timed(bar, parity, err, WAIT_LIMIT_NS);
 }
 
 // 4-D tiled load global -> shared, completion signalled on `bar` (no multicast)

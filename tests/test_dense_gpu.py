@@ -293,15 +293,20 @@ def test_bounded_wait_gives_up_and_is_reported():
     lib = cabi.lib()
     torch.cuda.synchronize()
     assert lib.l1attn_device_status() == 0
-    returned = torch.zeros(1, dtype=torch.int32, device="cuda")
+    returned = torch.zeros(2, dtype=torch.int32, device="cuda")
     pinned = torch.zeros(16, dtype=torch.int32).pin_memory()
     t0 = time.time()
     assert lib.l1attn_test_wait_timeout(3000, returned.data_ptr(), None) == 0
     assert lib.l1attn_device_status_async(pinned.data_ptr(), None) == 0  # the no-sync way to learn of it
     torch.cuda.synchronize()
     assert time.time() - t0 < 30.0
-    assert int(returned.item()) == 1, "the kernel must come back from the wait with `false`"
+    assert int(returned[0]) == 1, "the kernel must come back from the wait with `false`"
     assert int(pinned[0]) == 1
+    # duration of one failed poll: the hot loops poll 2^18 times before they look at the clock, which must stay
+    # in the range of a second
+    ns_per_poll = 3e6 / max(1, int(returned[1]))
+    print("failed mbarrier.try_wait poll: %.0f ns" % ns_per_poll)
+    assert ns_per_poll < 20000
     assert lib.l1attn_device_status() == -7 and b"bounded wait" in lib.l1attn_strerror(-7)
     assert lib.l1attn_device_status() == 0  # cleared by the read
     assert lib.l1attn_test_wait_timeout(0, returned.data_ptr(), None) == -1  # limits outside 1 us .. 100 ms are refused
@@ -321,7 +326,7 @@ def test_driver_raises_on_a_pending_timeout():
     l1attn_cuda_drv.forward(q, q)
     torch.cuda.synchronize()
     l1attn_cuda_drv.forward(q, q)  # nothing pending: fine
-    returned = torch.zeros(1, dtype=torch.int32, device="cuda")
+    returned = torch.zeros(2, dtype=torch.int32, device="cuda")
     assert lib.l1attn_test_wait_timeout(2000, returned.data_ptr(), torch.cuda.current_stream().cuda_stream) == 0
     l1attn_cuda_drv.forward(q, q)  # enqueued behind the probe; copies the (now set) word to the pinned word
     torch.cuda.synchronize()
