@@ -21,7 +21,7 @@ ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
 INC = os.path.join(ROOT, "include")
 LIB = os.path.join(HERE, "libl1attn_b200.so")
-CU_SOURCES = ["dense_fwd.cu", "dense_fwd_tma.cu", "dense_bwd.cu", "dense_bwd_tma.cu", "dense_ties.cu", "dense_softmax_v.cu", "sparse.cu", "coo.cu", "capi.cu", "tma.cu"]
+CU_SOURCES = ["dense_fwd.cu", "dense_fwd_tma.cu", "dense_bwd.cu", "dense_bwd_tma.cu", "dense_bwd_sv.cu", "dense_ties.cu", "dense_softmax_v.cu", "sparse.cu", "coo.cu", "capi.cu", "tma.cu"]
 DRIVERS = ["l1attn_cuda_drv", "l1attn_sparse_cuda_drv", "l1attn_sparse_bidi_cuda_drv"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]

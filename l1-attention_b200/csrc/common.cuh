@@ -71,10 +71,15 @@ int dense_fwd_tma_launch(const void *q, const void *k, void *attn, int bs, int n
 			 int dtype, cudaStream_t st);
 // tie_hdr: device tie header {count, overflow} or nullptr.  With a header whose overflow word is 0 every tile takes the
 // compare form (the listed ties are repaired afterwards by dense_tiefix_launch); otherwise the flags decide.
+// only_on_overflow: the kernel returns at once unless the header's overflow word is set (the single-visit kernel ran before it)
 int dense_bwd_tma_launch(const void *d_attn, const void *q, const void *k, void *d_q, void *d_k, int bs, int n_tok,
-			 int n_heads, int width, int dtype, const unsigned char *exact_flags, const int *tie_hdr, cudaStream_t st);
+			 int n_heads, int width, int dtype, const unsigned char *exact_flags, const int *tie_hdr,
+			 int only_on_overflow, cudaStream_t st);
+int dense_bwd_sv_launch(const void *d_attn, const void *q, const void *k, void *d_q, void *d_k, const int *tie_hdr,
+			void *part, int bs, int n_tok, int n_heads, int width, int dtype, cudaStream_t st);
+// dk_sign: +1 after the two-pass kernel (a tie counted as -scale g in d_k), -1 after the single-visit kernel (+scale g)
 int dense_tiefix_launch(const void *d_attn, void *d_q, void *d_k, const unsigned char *scratch, int bs, int n_tok,
-			int n_heads, int width, cudaStream_t st);
+			int n_heads, int width, int dk_sign, cudaStream_t st);
 int dense_ties_launch(const float *q, const float *k, unsigned char *scratch, int bs, int n_tok, int n_heads, int width,
 		      cudaStream_t st);
 // scratch: dense_bwd_scratch_bytes() bytes of device memory, or nullptr (then every tile runs the exact loop)

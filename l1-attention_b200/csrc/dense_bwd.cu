@@ -177,7 +177,7 @@ size_t dense_bwd_scratch_bytes(int bs, int n_tok, int n_heads, int width, int dt
 {
 	if (dtype != L1ATTN_F32 || bs <= 0 || n_tok <= 0 || n_heads <= 0 || width <= 0)
 		return 16;
-	return bwd_scratch_layout(bs, n_tok, n_heads, width).bytes; // tie flags, tie header, tie list
+	return bwd_scratch_layout(bs, n_tok, n_heads, width).bytes; // tie flags, tie header, tie list, shares of d_k
 }
 
 int dense_bwd_launch(const void *d_attn, const void *q, const void *k, void *d_q, void *d_k, void *scratch, int bs,
@@ -186,32 +186,55 @@ int dense_bwd_launch(const void *d_attn, const void *q, const void *k, void *d_q
 	if (bs == 0 || n_tok == 0 || n_heads == 0 || width == 0)
 		return L1ATTN_OK;
 	static const bool no_tma = getenv("L1ATTN_NO_TMA") != nullptr; // debugging aid: force the generic kernel
+	static const bool no_sv = getenv("L1ATTN_NO_SV") != nullptr;   // debugging aid: force the two-pass kernel
 	if (!no_tma) {
 		// With scratch the tie detector runs first: it lists every exact tie q == k (and marks tiles, for the case
-		// that the list overflows -- a device-side fact, no host round trip).  The fast kernel then takes the
-		// compare form on every tile and the listed terms are repaired afterwards; on overflow it runs the exact
-		// loop where flagged tiles meet.  Without scratch (or when the detector does not apply) every tile
-		// runs the exact loop.
+		// that the list overflows -- a device-side fact, no host round trip).  Then the single-visit kernel computes
+		// both gradients with the compare form and the listed terms are repaired afterwards.  If the list overflowed
+		// that kernel returns at once and the two-pass kernel, gated on the same word, runs its exact loop where
+		// flagged tiles meet.  Without scratch (or when the detector does not apply) the two-pass kernel runs every
+		// tile with the exact loop.
 		unsigned char *flags = nullptr;
 		const int *tie_hdr = nullptr;
-		if (scratch && dtype == L1ATTN_F32 && width % 4 == 0 && n_heads % 4 == 0 && aligned(scratch, 16)) {
+		int sv = 0;
+		if (scratch && dtype == L1ATTN_F32 && width % 4 == 0 && n_heads % 4 == 0 && aligned(scratch, 256)) {
 			const int trc = dense_ties_launch((const float *)q, (const float *)k, (unsigned char *)scratch, bs, n_tok,
 							  n_heads, width, st);
 			if (trc < 0)
 				return trc;
 			if (trc == 0) {
 				const BwdScratchLayout sl = bwd_scratch_layout(bs, n_tok, n_heads, width);
-				flags = (unsigned char *)scratch + sl.flags;
-				tie_hdr = (const int *)((unsigned char *)scratch + sl.hdr);
+				unsigned char *sc = (unsigned char *)scratch;
+				flags = sc + sl.flags;
+				tie_hdr = (const int *)(sc + sl.hdr);
+				// Both fast kernels are persistent with equal-sized work items, so the last wave of items decides how
+				// full the GPU stays: the single-visit kernel (4 heads x 32 columns x 128 query rows per item, ~8 %
+				// faster per term) runs unless its item count leaves the SMs markedly emptier than the two-pass
+				// kernel's (8 heads x 64 columns x 32 rows per item and gradient) would.
+				int dev = 0, sms = 148;
+				(void)cudaGetDevice(&dev);
+				(void)cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+				auto fill = [&](double items) { return items / (double((long long)((items + sms - 1) / sms)) * sms); };
+				const double it_sv = double(bs) * ((n_heads + 3) / 4) * ((width + 31) / 32) * ((n_tok + 127) / 128);
+				const double it_tp = 2.0 * bs * ((n_heads + 7) / 8) * ((width + 63) / 64) * ((n_tok + 31) / 32);
+				if (!no_sv && 1.08 * fill(it_sv) >= fill(it_tp)) {
+					const int frc = dense_bwd_sv_launch(d_attn, q, k, d_q, d_k, tie_hdr, sc + sl.part, bs, n_tok, n_heads, width,
+									    dtype, st);
+					if (frc < 0)
+						return frc;
+					sv = frc == 0;
+				}
 			}
 		}
-		const int rc = dense_bwd_tma_launch(d_attn, q, k, d_q, d_k, bs, n_tok, n_heads, width, dtype, flags, tie_hdr, st);
+		const int rc = dense_bwd_tma_launch(d_attn, q, k, d_q, d_k, bs, n_tok, n_heads, width, dtype, flags, tie_hdr, sv, st);
 		if (rc < 0)
 			return rc;
 		if (rc == 0)
 			return tie_hdr ? dense_tiefix_launch(d_attn, d_q, d_k, (const unsigned char *)scratch, bs, n_tok, n_heads,
-							     width, st)
+							     width, sv ? -1 : 1, st)
 				       : L1ATTN_OK;
+		if (sv)
+			return L1ATTN_ERR_CUDA; // cannot happen: both fast kernels accept the same shapes and alignments
 	}
 	if (dtype == L1ATTN_F32)
 		return launch<float, 8, 4, 2>((const float *)d_attn, (const float *)q, (const float *)k, (float *)d_q,

@@ -36,14 +36,16 @@ inline BwdFlagLayout bwd_flag_layout(int bs, int n_tok, int n_heads, int width)
 	return l;
 }
 
-// ---- listed ties ----
+// ---- listed ties, single-visit backward ----
 constexpr int BWD_TIE_CAP = 4096; // listed ties per call; more set the overflow word and the flagged exact loops run
+constexpr int BWD_SV_TX = 128;    // query rows per work item of the single-visit kernel: d_k leaves it as ceil(n_tok / 128) shares
 
 // Caller-provided scratch of the dense backward, in this order (every part 256-byte aligned):
-//   tie flags | tie header {count, overflow} | tie list uint4[BWD_TIE_CAP]
+//   tie flags | tie header {count, overflow} | tie list uint4[BWD_TIE_CAP] | shares of d_k
 // The flags and the header are adjacent so that one memset clears both.
 struct BwdScratchLayout {
-	size_t flags, hdr, ties, bytes; // offsets, total
+	size_t flags, hdr, ties, part, bytes; // offsets, total
+	int ntb;
 };
 inline BwdScratchLayout bwd_scratch_layout(int bs, int n_tok, int n_heads, int width)
 {
@@ -52,7 +54,9 @@ inline BwdScratchLayout bwd_scratch_layout(int bs, int n_tok, int n_heads, int w
 	l.flags = 0;
 	l.hdr = pad(bwd_flag_layout(bs, n_tok, n_heads, width).bytes());
 	l.ties = l.hdr + 256;
-	l.bytes = l.ties + size_t(BWD_TIE_CAP) * 16;
+	l.part = l.ties + size_t(BWD_TIE_CAP) * 16;
+	l.ntb = (n_tok + BWD_SV_TX - 1) / BWD_SV_TX;
+	l.bytes = l.part + pad(size_t(l.ntb) * bs * n_tok * n_heads * width * 4);
 	return l;
 }
 } // namespace l1b

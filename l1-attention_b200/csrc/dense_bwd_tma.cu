@@ -144,8 +144,11 @@ dense_bwd_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_cons
 		     const __grid_constant__ CUtensorMap gmap0, const __grid_constant__ CUtensorMap gmap1,
 		     const float *__restrict__ q, const float *__restrict__ k, float *__restrict__ d_q,
 		     float *__restrict__ d_k, const unsigned char *__restrict__ flags, BwdFlagLayout fl, int n_tok,
-		     int n_heads, int width, float scale, BwdWork wk, const int *__restrict__ tie_hdr, int *err)
+		     int n_heads, int width, float scale, BwdWork wk, const int *__restrict__ tie_hdr, int only_on_overflow,
+		     int *err)
 {
+	if (only_on_overflow != 0 && tie_hdr[1] == 0)
+		return; // the single-visit kernel (dense_bwd_sv.cu) has computed this call
 	// Every tie of this call is in the detector's list (no overflow): all tiles take the compare form and the fix
 	// kernel repairs the listed terms afterwards.  Otherwise the per-tile flags choose the exact loop.
 	const int listed = (tie_hdr != nullptr && tie_hdr[1] == 0) ? 1 : 0;
@@ -312,7 +315,8 @@ dense_bwd_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_cons
 // Returns L1ATTN_OK, a negative error, or 1 when this path does not apply.
 // flags: device tie flags laid out by bwd_flag_layout() and filled by dense_ties_launch(), or nullptr = all exact.
 int dense_bwd_tma_launch(const void *d_attn, const void *q, const void *k, void *d_q, void *d_k, int bs, int n_tok,
-			 int n_heads, int width, int dtype, const unsigned char *flags, const int *tie_hdr, cudaStream_t st)
+			 int n_heads, int width, int dtype, const unsigned char *flags, const int *tie_hdr, int only_on_overflow,
+			 cudaStream_t st)
 {
 	if (dtype != L1ATTN_F32)
 		return 1;
@@ -357,7 +361,7 @@ int dense_bwd_tma_launch(const void *d_attn, const void *q, const void *k, void 
 	const BwdFlagLayout fl = bwd_flag_layout(bs, n_tok, n_heads, width);
 	dense_bwd_tma_kernel<<<grid, NTHREADS, smem, st>>>(qmap, kmap, gmap0, gmap1, (const float *)q, (const float *)k,
 							    (float *)d_q, (float *)d_k, flags, fl, n_tok, n_heads, width, scale,
-							    wk, tie_hdr, err);
+							    wk, tie_hdr, (tie_hdr != nullptr && only_on_overflow) ? 1 : 0, err);
 	L1B_LAUNCH_CHECK();
 	return L1ATTN_OK;
 }

@@ -216,15 +216,16 @@ int launch_nc(const float *q, const float *k, unsigned char *flags, int bs, int 
 }
 
 // Repairs the listed ties after the compare-form backward.  That form counts a term as +g where a > b and as -g
-// otherwise, so a tie q == k (which must contribute nothing) has put -scale * g into d_q[b][t][h][w] and into
-// d_k[b][s][h][w]: both get scale * g[b][s][t][h] back.
+// otherwise, so a tie q == k (which must contribute nothing) has put -scale * g into d_q[b][t][h][w]: it gets
+// scale * g[b][s][t][h] back.  d_k[b][s][h][w] received -scale * g from the two-pass kernel (which compares k > q
+// for it) and +scale * g from the single-visit kernel (one compare q > k for both): dk_sign = +1 / -1.
 // One CTA.  The list arrives in no particular order (the detector appends with an atomic counter), so it is
 // ranked first -- by (column, query row, source row) for d_q, by (column, source row, query row) for d_k -- and
 // every run of entries that hit the same output element is summed by one thread in rank order: the result
 // does not depend on the order of arrival.
 __global__ void __launch_bounds__(1024)
 dense_tiefix_kernel(const int *__restrict__ tie_hdr, const uint4 *__restrict__ ties, const float *__restrict__ g,
-		    float *__restrict__ d_q, float *__restrict__ d_k, int n_tok, int n_heads, int width, float scale)
+		    float *__restrict__ d_q, float *__restrict__ d_k, int n_tok, int n_heads, int width, float scale, float dk_scale)
 {
 	extern __shared__ __align__(16) unsigned char fix_smem[];
 	if (tie_hdr[1] != 0)
@@ -280,7 +281,7 @@ dense_tiefix_kernel(const int *__restrict__ tie_hdr, const uint4 *__restrict__ t
 					break;
 				sum += gval(c);
 			}
-			d_k[(size_t(a.x / hwn) * n_tok + a.z) * row + a.x % hwn] += scale * sum;
+			d_k[(size_t(a.x / hwn) * n_tok + a.z) * row + a.x % hwn] += dk_scale * sum;
 		}
 	}
 }
@@ -317,7 +318,7 @@ int dense_ties_launch(const float *q, const float *k, unsigned char *scratch, in
 
 // Enqueue after the compare-form backward: adds the listed ties' terms back (no-op when the list overflowed).
 int dense_tiefix_launch(const void *d_attn, void *d_q, void *d_k, const unsigned char *scratch, int bs, int n_tok,
-			int n_heads, int width, cudaStream_t st)
+			int n_heads, int width, int dk_sign, cudaStream_t st)
 {
 	const BwdScratchLayout sl = bwd_scratch_layout(bs, n_tok, n_heads, width);
 	const size_t smem = size_t(BWD_TIE_CAP) * (16 + 8);
@@ -325,7 +326,7 @@ int dense_tiefix_launch(const void *d_attn, void *d_q, void *d_k, const unsigned
 	dense_tiefix_kernel<<<1, 1024, smem, st>>>(reinterpret_cast<const int *>(scratch + sl.hdr),
 						   reinterpret_cast<const uint4 *>(scratch + sl.ties), (const float *)d_attn,
 						   (float *)d_q, (float *)d_k, n_tok, n_heads, width,
-						   float(-1.0 / sqrt(double(width))));
+						   float(-1.0 / sqrt(double(width))), float(-dk_sign / sqrt(double(width))));
 	L1B_LAUNCH_CHECK();
 	return L1ATTN_OK;
 }
