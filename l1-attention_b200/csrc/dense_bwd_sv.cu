@@ -48,7 +48,7 @@ constexpr int SV_GTSTAGE = 41984;                         // GT | B | CS, padded
 constexpr int SV_PK_BYTES = SV_NCW * SV_TY * 32 * 4;      // 32768: [warp][s][lane] partial d_k sums of one tile
 static_assert(SV_GT_BYTES + SV_B_BYTES + SV_CS_BYTES <= SV_GTSTAGE, "stage layout");
 static_assert(SV_TX == (SV_NCW / SV_HG) * SV_XR && SV_TY == 4 * (SV_NCW / SV_HG) && SV_TY == SV_NCW, "row groups, one row per warp");
-constexpr size_t SV_SMEM = 2 * SV_RAW_BYTES + 2 * SV_GTSTAGE + 2 * SV_PK_BYTES + SV_NCW * 32 * 4 + 1024;
+constexpr size_t SV_SMEM = 2 * SV_RAW_BYTES + 2 * SV_GTSTAGE + 2 * SV_PK_BYTES + SV_NCW * 32 * 4 + 4 * SV_CS_BYTES + 1024;
 
 struct SvWork {
 	unsigned nws, ntb, nhg, total;
@@ -100,32 +100,29 @@ struct SvCursor {
 };
 
 // One tile (SV_TY source rows) for a compute thread: 32 query rows of its column against the tile's k values.
-__device__ __forceinline__ void sv_tile_compute(const unsigned char *gts, float *pkw, int xg, int h, int lane, float csw,
+__device__ __forceinline__ void sv_tile_compute(const unsigned char *gts, float *pkw, int xg, int h, int lane,
 						const float (&a)[SV_XR], float (&acc)[SV_XR], float &rsq)
 {
 	const float4 *GT = reinterpret_cast<const float4 *>(gts) + h * (SV_TX / 4) + xg * (SV_XR / 4);
 	const float *GL = reinterpret_cast<const float *>(gts) + h * SV_TX + xg * SV_XR + lane;
 	const float *B = reinterpret_cast<const float *>(gts + SV_GT_BYTES) + h * SV_WS + lane;
-	const float *CS = reinterpret_cast<const float *>(gts + SV_GT_BYTES + SV_B_BYTES) + h;
-#pragma unroll 2
+#pragma unroll 4
 	for (int s = 0; s < SV_TY; s++) {
 		const float bv = B[s * (SV_HG * SV_WS)];
-		float pk0 = 0.f, pk1 = 0.f;
+		float pk = 0.f;
 #pragma unroll
 		for (int i4 = 0; i4 < SV_XR / 4; i4++) {
 			const float4 g = GT[s * (SV_HG * SV_TX / 4) + i4];
 			// four compares, then the eight predicated adds they feed
 			asm("{\n\t.reg .pred p0, p1, p2, p3;\n\t"
-			    "setp.gt.f32 p0, %6, %10;\n\tsetp.gt.f32 p1, %7, %10;\n\tsetp.gt.f32 p2, %8, %10;\n\tsetp.gt.f32 p3, %9, %10;\n\t"
-			    "@p0 add.f32 %0, %0, %11;\n\t@p1 add.f32 %1, %1, %12;\n\t@p2 add.f32 %2, %2, %13;\n\t@p3 add.f32 %3, %3, %14;\n\t"
-			    "@p0 add.f32 %4, %4, %11;\n\t@p1 add.f32 %5, %5, %12;\n\t@p2 add.f32 %4, %4, %13;\n\t@p3 add.f32 %5, %5, %14;\n\t}"
-			    : "+f"(acc[i4 * 4]), "+f"(acc[i4 * 4 + 1]), "+f"(acc[i4 * 4 + 2]), "+f"(acc[i4 * 4 + 3]), "+f"(pk0), "+f"(pk1)
+			    "setp.gt.f32 p0, %5, %9;\n\tsetp.gt.f32 p1, %6, %9;\n\tsetp.gt.f32 p2, %7, %9;\n\tsetp.gt.f32 p3, %8, %9;\n\t"
+			    "@p0 add.f32 %0, %0, %10;\n\t@p1 add.f32 %1, %1, %11;\n\t@p2 add.f32 %2, %2, %12;\n\t@p3 add.f32 %3, %3, %13;\n\t"
+			    "@p0 add.f32 %4, %4, %10;\n\t@p1 add.f32 %4, %4, %11;\n\t@p2 add.f32 %4, %4, %12;\n\t@p3 add.f32 %4, %4, %13;\n\t}"
+			    : "+f"(acc[i4 * 4]), "+f"(acc[i4 * 4 + 1]), "+f"(acc[i4 * 4 + 2]), "+f"(acc[i4 * 4 + 3]), "+f"(pk)
 			    : "f"(a[i4 * 4]), "f"(a[i4 * 4 + 1]), "f"(a[i4 * 4 + 2]), "f"(a[i4 * 4 + 3]), "f"(bv), "f"(g.x), "f"(g.y), "f"(g.z),
 			      "f"(g.w));
 		}
-		// the first row group carries the item's -1/2 sum_t g (csw = -1/2 there, 0 in the other groups: no branch, no
-		// predicate): twice the sum of the four partials is then 2 sum p g - sum g
-		pkw[s * 32] = fmaf(csw, CS[s * SV_HG], pk0 + pk1);
+		pkw[s * 32] = pk; // (one accumulator: its 32 dependent adds are spread over the ~110 instructions of the row)
 		rsq += GL[s * (SV_HG * SV_TX)]; // lane l sums g of query row l of the group: the row sums, spread over the lanes
 	}
 }
@@ -151,6 +148,7 @@ dense_bwd_sv_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_const
 	unsigned char *gts = raw + 2 * SV_RAW_BYTES;
 	float *pkbase = reinterpret_cast<float *>(gts + 2 * SV_GTSTAGE);
 	float *rowsum = pkbase + 2 * (SV_PK_BYTES / 4); // [warp][lane] row sums on their way to the d_q store
+	float *csring = rowsum + SV_NCW * 32;             // [tile & 3][s][h]: sum over the item's query rows of g, for the reducer
 	__shared__ __align__(8) SvBars bars;
 	__shared__ SvCursor cur_raw, cur_kb;
 
@@ -173,7 +171,6 @@ dense_bwd_sv_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_const
 	__syncthreads();
 	const size_t row = size_t(n_heads) * width;
 	const int xg = warp >> 2, h = warp & 3;
-	const float csw = xg == 0 ? -0.5f : 0.f;
 	int dead = 0;
 
 	// thread 0 only: request the next raw gradient tile / the next tile of k rows (no-ops past the last tile)
@@ -246,7 +243,7 @@ dense_bwd_sv_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_const
 			kc += __shfl_xor_sync(0xffffffffu, kc, 2);
 			kc += __shfl_xor_sync(0xffffffffu, kc, 1);
 			if ((ln & 7) == 0) // lanes 0, 8, 16, 24 hold heads 0, 1, 2, 3
-				reinterpret_cast<float *>(gts + st * SV_GTSTAGE + SV_GT_BYTES + SV_B_BYTES)[warp * SV_HG + (ln >> 3)] = kc;
+				csring[(m & 3u) * (SV_TY * SV_HG) + warp * SV_HG + (ln >> 3)] = kc; // read two steps later: four slots keep writer and reader apart
 #endif
 		}
 		__syncwarp();
@@ -267,9 +264,11 @@ dense_bwd_sv_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_const
 	// thread's column is out of range), and its first source row
 	float *red_pp = nullptr;
 	int red_s0 = -1, red_rows = 0; // red_rows: source rows of that tile this thread may store (0: column out of range)
-	auto reduce_prev = [&](unsigned slot) {
-		// this warp's four source rows of the tile: s = xg, xg+4, xg+8, xg+12; the four row groups' partials in order
-		const float *P = pkbase + slot * (SV_PK_BYTES / 4) + h * (SV_TY * 32) + lane;
+	auto reduce_prev = [&](unsigned tile_no) {
+		// this warp's four source rows of the tile: s = xg, xg+4, xg+8, xg+12; the four row groups' partials in order;
+		// share = 2 sum p g - sum g
+		const float *P = pkbase + (tile_no & 1u) * (SV_PK_BYTES / 4) + h * (SV_TY * 32) + lane;
+		const float *C = csring + (tile_no & 3u) * (SV_TY * SV_HG) + h;
 #pragma unroll
 		for (int j = 0; j < 4; j++) {
 			const int s = xg + 4 * j;
@@ -279,7 +278,7 @@ dense_bwd_sv_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_const
 			v += ps[2 * SV_HG * SV_TY * 32];
 			v += ps[3 * SV_HG * SV_TY * 32];
 			if (s < sv_opaque(red_rows))
-				red_pp[size_t(red_s0 + s) * row] = 2.f * v;
+				red_pp[size_t(red_s0 + s) * row] = fmaf(2.f, v, -C[s * SV_HG]);
 		}
 	};
 	for (unsigned item = blockIdx.x; item < wk.total; item += gridDim.x) {
@@ -311,10 +310,10 @@ dense_bwd_sv_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_const
 				issue_raw(); // tile n + 2 into the raw slot tile n was transposed out of
 				issue_kb();  // k rows of tile n + 1 into the stage the math of tile n - 1 has left
 			}
-			sv_tile_compute(gts + st * SV_GTSTAGE, pkbase + st * (SV_PK_BYTES / 4) + warp * (SV_TY * 32) + lane, xg, h, lane, csw, a, acc, rsq);
+			sv_tile_compute(gts + st * SV_GTSTAGE, pkbase + st * (SV_PK_BYTES / 4) + warp * (SV_TY * 32) + lane, xg, h, lane, a, acc, rsq);
 #ifndef SV_EXP_NO_REDUCE
 			if (sv_opaque(red_s0) >= 0)
-				reduce_prev(unsigned(st ^ 1));
+				reduce_prev(n - 1u);
 #endif
 			red_pp = item_pp;
 			red_s0 = tile * SV_TY;
@@ -343,7 +342,7 @@ dense_bwd_sv_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_const
 	if (n_tiles > 0) { // the last tile's partials: complete once every warp has made its arrival for the phase after it
 		if (dead == 0 && !mbar_wait(&bars.gt_full[n & 1u], (n >> 1) & 1u, err))
 			dead = 1;
-		reduce_prev(unsigned((n & 1u) ^ 1u));
+		reduce_prev(n - 1u);
 	}
 }
 

@@ -7,9 +7,9 @@
 // backward runs its exact loop where its marked x rows meet a marked y tile and the short loop elsewhere.
 //
 // Exact, in two steps.  One CTA handles NC width columns of one (batch, head):
-//   1. filter: every k value sets two bits (two hash functions) of its column's bitmap in shared
-//      memory; a q value whose two bits are both set is a candidate.  With 64 bits per token (up to
-//      4096 tokens) the false-candidate rate is ~1/1024 per value: about four candidates per CTA;
+//   1. filter: every k value sets three bits of one hashed word of its column's bitmap in shared
+//      memory; a q value whose three bits are all set is a candidate.  With 64 bits per token (up to
+//      4096 tokens) the false-candidate rate is ~1/1000 per value: about four candidates per CTA;
 //   2. proof: every candidate value is compared, bit pattern against bit pattern, with all k values
 //      of its column (held in registers by the threads that loaded them).  Matching k rows and
 //      the candidate's q row are the rows that tie.
@@ -28,8 +28,16 @@ constexpr int TB = 4;    // tokens per thread per batch
 constexpr int CAP = 512; // candidate list entries per CTA
 
 __device__ __forceinline__ unsigned canon(float x) { return __float_as_uint(x + 0.0f); }
-__device__ __forceinline__ unsigned hash1(unsigned b, int sh) { return (b * 0x9E3779B1u) >> sh; }
-__device__ __forceinline__ unsigned hash2(unsigned b, int sh) { return ((b ^ (b >> 15)) * 0xC2B2AE3Du) >> sh; }
+// The three filter bits of a value lie in ONE 32-bit word of its column's bitmap: the word comes from the top bits of
+// one hash, the bit positions from a second one.  One shared-memory atomic per k value and one load per q value (bits
+// in two words cost twice that, and the shared-memory atomics and the proof loop over the candidates are what
+// bounds this kernel; two bits in one word gave three times the false candidates and a 35 % slower kernel).
+__device__ __forceinline__ unsigned hash_word(unsigned b, int sh) { return (b * 0x9E3779B1u) >> sh; } // sh = 32 - log2(words)
+__device__ __forceinline__ unsigned hash_bits(unsigned b)
+{
+	const unsigned x = (b ^ (b >> 15)) * 0xC2B2AE3Du;
+	return (1u << (x >> 27)) | (1u << ((x >> 22) & 31u)) | (1u << ((x >> 17) & 31u));
+}
 
 template <int NC>
 __device__ __forceinline__ void load_batch(const float *base, size_t row, int t0, int n_tok, int ncol, float (&v)[TB][NC])
@@ -67,7 +75,7 @@ __global__ void __launch_bounds__(NT_MAX) dense_ties_kernel(const float *__restr
 	__shared__ int n_cand, overflow;
 	const int NT = blockDim.x;
 	const unsigned words = 1u << (log2bits - 5);
-	const int sh = 32 - log2bits;
+	const int sh = 32 - (log2bits - 5);
 	const int ncg = (width + NC - 1) / NC;
 	unsigned r = blockIdx.x;
 	const int w0 = int(r % ncg) * NC;
@@ -103,9 +111,8 @@ __global__ void __launch_bounds__(NT_MAX) dense_ties_kernel(const float *__restr
 			for (int j = 0; j < NC; j++) {
 				const float x = v[i][j];
 				if (t0 + i * NT < n_tok && j < ncol && x == x) {
-					const unsigned bits = canon(x), h1 = hash1(bits, sh), h2 = hash2(bits, sh);
-					atomicOr(&bitmap[j * words + (h1 >> 5)], 1u << (h1 & 31));
-					atomicOr(&bitmap[j * words + (h2 >> 5)], 1u << (h2 & 31));
+					const unsigned bits = canon(x);
+					atomicOr(&bitmap[j * words + hash_word(bits, sh)], hash_bits(bits));
 				}
 			}
 	}
@@ -122,10 +129,9 @@ __global__ void __launch_bounds__(NT_MAX) dense_ties_kernel(const float *__restr
 					const float x = qv[i][j];
 					const int t = t0 + i * NT;
 					if (t < n_tok && j < ncol && x == x) {
-						const unsigned bits = canon(x), h1 = hash1(bits, sh);
-						if (bitmap[j * words + (h1 >> 5)] >> (h1 & 31) & 1u) {
-							const unsigned h2 = hash2(bits, sh);
-							if (bitmap[j * words + (h2 >> 5)] >> (h2 & 31) & 1u) {
+						const unsigned bits = canon(x), want = hash_bits(bits);
+						if ((bitmap[j * words + hash_word(bits, sh)] & want) == want) {
+							{
 								const int idx = atomicAdd(&n_cand, 1);
 								if (idx < CAP) {
 									cand_bits[idx] = bits;
