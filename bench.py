@@ -606,15 +606,15 @@ def roofline_of(wl, t, pk, clocks, l2_gbs=None):
     bs, n, h, w = wl["shape"]
     fwd_ms, bwd_ms = t["fwd_ms"], t["bwd_ms"]
     if wl["kind"] == "dense":
-        # dominant kernel: the backward launch (both gradient passes; its CUDA-event time bwd_ms also holds the
-        # tie detector and the tie fix).  Algorithmic HBM bytes per launch: d_attn read once per pass, q and k
-        # read per pass, both gradients written.
-        alg_bytes = 4.0 * (2 * bs * n * n * h + 6 * bs * n * h * w)
-        roof = {"bound": "hbm", "kernel": "dense_bwd_tma_kernel", "achieved": alg_bytes / (bwd_ms * 1e-3) / 1e9,
+        # dominant kernel: the single-visit backward (dense_bwd_sv_kernel; the CUDA-event time bwd_ms also holds the tie
+        # detector, the sum of the d_k shares and the tie fix, ~8 % of it).  Algorithmic HBM bytes per backward: d_attn,
+        # q and k read once, both gradients written once.
+        alg_bytes = 4.0 * (bs * n * n * h + 4 * bs * n * h * w)
+        roof = {"bound": "hbm", "kernel": "dense_bwd_sv_kernel", "achieved": alg_bytes / (bwd_ms * 1e-3) / 1e9,
                 "peak": pk["hbm_gbs"], "unit": "GB/s", "peak_source": pk["source"],
                 # ncu dram__bytes_read+write of this kernel at B=2,T=1024,H=16,W=64 (profiles/), scaled by batch
                 "traffic": (DENSE_BWD_TRAFFIC_B2 * bs / 2.0) if (n, h, w) == (1024, 16, 64) and DENSE_BWD_TRAFFIC_B2 else None,
-                "note": "the kernel is FP32/ALU-pipe bound, not HBM bound: see alu_roofline"}
+                "note": "the kernel is bound by instruction issue, not by HBM: see alu_roofline"}
         roof["frac"] = roof["achieved"] / roof["peak"]
         mhz = (clocks or {}).get("sm_max_mhz") or pk["sm_max_mhz"]
         alu_peak = SM_COUNT * FP32_LANES * mhz * 1e6
@@ -642,10 +642,11 @@ def roofline_of(wl, t, pk, clocks, l2_gbs=None):
     return roof, None
 
 
-# kernels of this library per dense step: forward; tie detector; backward (both gradients); tie fix
-DENSE_LAUNCHES_PER_STEP = 4
+# kernels of this library per dense step: forward; tie detector; single-visit backward; sum of the d_k shares;
+# two-pass kernel (returns at once unless the tie list overflowed); tie fix
+DENSE_LAUNCHES_PER_STEP = 6
 # ncu dram__bytes_read.sum + dram__bytes_write.sum per launch at the profiling sizes (profiles/*.md)
-DENSE_BWD_TRAFFIC_B2 = 314.9e6
+DENSE_BWD_TRAFFIC_B2 = 198.8e6
 SPARSE_TRAFFIC_B2 = 226.9e6
 
 
