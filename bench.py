@@ -16,10 +16,17 @@ metric: dense  Gop/s          = B*H*T^2*W / (t_fwd + t_bwd), one op = one |q-k| 
 
 value  : device-resident inputs, CUDA-event timed, max over ranks.
 e2e    : the same step through the C ABI's host-buffer entry points (pinned host memory in,
-         host memory out; copies inside the timed region).
+         host memory out; copies inside the timed region; batch items pipelined over the
+         library's streams).
 N > 1  : one process per GPU (torchrun); every rank runs the full workload on its own data
          (weak scaling; the path has no cross-shard reduction, so no data-path collective);
-         value = units of all ranks / slowest rank's time.
+         value = units of all ranks / slowest rank's time.  "strong" in the same line: the
+         workload's ONE batch split over the ranks ((batch, head group) for dense; batch items,
+         or dst-token ranges with one all_reduce of d_k, d_v when there are fewer items than
+         ranks, for sparse).
+Extra keys of the default run (--no-extras drops them): "sparse_cfg4" (the sparse workload's
+own record), "reference_cuda" (the reference's GPU extension rebuilt for sm_100, same tensors,
+when it was built into oracle/_ref), "module_ms" (the step through the torch.autograd modules).
 --impl reference : the reference's own CPU implementation (compiled from its sources into
          oracle/_ref, else the C restatement) on a bounded sample of the same workload.
 """

@@ -99,13 +99,15 @@ int l1attn_dense_fwd(const void *q, const void *k, void *attn,
  * d_q[b][t][h][w] =  scale * sum_s sign(q[b][t][h][w]-k[b][s][h][w]) * d_attn[b][s][t][h]
  * d_k[b][s][h][w] = -scale * sum_t sign(q[b][t][h][w]-k[b][s][h][w]) * d_attn[b][s][t][h]
  * with scale = -1/sqrt(width) and sign(0) = 0.  Deterministic (no atomics).
- * `scratch`: device buffer of l1attn_dense_bwd_scratch_bytes() bytes (16-byte aligned, ~100 KB), or NULL.
+ * `scratch`: device buffer of l1attn_dense_bwd_scratch_bytes() bytes (256-byte aligned), or NULL.
  * In fp32 a detector kernel proves every exact tie q == k -- the one case the fast inner loop (compare +
- * predicated add) gets wrong -- and writes them there as a list, which a fix kernel applies after the
+ * predicated adds) gets wrong -- and writes them there as a list, which a fix kernel applies after the
  * backward, plus one flag per tile for the case that the list overflows (zero-padded tokens, q == k:
- * the flagged tiles then take an exact loop).  With NULL every tile takes the exact loop (same results,
- * more than twice the time in fp32).  Contents need no initialisation and mean nothing after the call;
- * calls that share a scratch buffer must not overlap on the GPU.
+ * flagged tiles then take an exact loop).  The rest of the buffer receives the shares of d_k that the
+ * single-visit kernel leaves per block of 128 query rows: ceil(n_tok / 128) * sizeof(d_k) bytes, i.e.
+ * about width / 128 times the size of d_attn.  With NULL every tile takes the exact loop and no scratch is
+ * needed (same results, about 2.7 times the time in fp32).  Contents need no initialisation and mean
+ * nothing after the call; calls that share a scratch buffer must not overlap on the GPU.
  * Replaces l1attn_cuda_drv.backward (cuda/l1attn_cuda_drv.cpp:67-104) and
  * l1attn_cuda_backward{,32,64} (cuda/l1attn_cuda_kernel.cu:559-685).
  */
