@@ -46,6 +46,7 @@ WORKLOADS = {
     "dense_cfg2": dict(kind="dense", shape=(16, 1024, 16, 64)),
     "dense_cfg3": dict(kind="dense", shape=(2, 4096, 8, 128)),
     "dense_cfg1": dict(kind="dense", shape=(4, 128, 8, 64)),
+    "dense_long1": dict(kind="dense", shape=(1, 4096, 8, 128)),  # one long-context item: on 4 GPUs the ranks tile its scores 2 x 2
     "dense_small": dict(kind="dense", shape=(2, 1024, 16, 64)),  # profiling size: 134 MB of scores, > L2
     "sparse_small": dict(kind="sparse", shape=(2, 4096, 8, 64), fan=31),
     "sparse_cfg4": dict(kind="sparse", shape=(8, 4096, 8, 64), fan=31),
@@ -804,7 +805,7 @@ def run_ours(args, wl):
                 line["sparse_cfg4"]["strong"] = st
 
     # ---- strong scaling beside the weak number: the SAME global workload dealt out over the ranks
-    if secondary and world > 1 and args.scaling == "weak":
+    if not args.no_extras and world > 1 and args.scaling == "weak":
         line_strong = run_strong(torch, dist, cabi, shard, args, wl, rank, world, dev, sync_all)
         if rank == 0:
             line["strong"] = line_strong
@@ -820,20 +821,42 @@ def run_ours(args, wl):
 
 def run_strong(torch, dist, cabi, shard, args, wl, rank, world, dev, sync_all):
     """The workload at its stated global size, partitioned over the ranks (l1attn_shard): dense by (batch, head
-    group) with shard-resident outputs and no collective; sparse by batch item when there are enough of them,
+    group) with shard-resident outputs and no collective -- with fewer batch items than ranks also by square
+    blocks of an item's scores (one all-reduce each of d_q and d_k), reporting the faster; sparse by batch item when there are enough of them,
     else by dst-token range with ONE all-reduce of d_k and d_v.  Returns the record for rank 0."""
     kind, shape = wl["kind"], wl["shape"]
     bs, n, h, w = shape
     unit = "Gop/s" if kind == "dense" else "Gedge-inst/s"
     if kind == "dense":
+        units = float(bs) * h * n * n * w
+        out = {}
+        if bs < world:
+            # fewer batch items than ranks: also the square-block partition (all heads of the kernels' work items
+            # stay busy; d_q and d_k partial sums meet in one all-reduce each)
+            plan = shard.DenseGridShard(bs, n, h, rank, world)
+            m = plan.me
+            lshape = (m["b1"] - m["b0"], m["t1"] - m["t0"], m["h1"] - m["h0"], w)
+            gwl = setup_dense(torch, cabi, lshape, dev, 2000 + rank)
+            gattn = torch.empty((lshape[0], lshape[1], lshape[1], lshape[2]), device=dev)
+            gout = (torch.empty_like(gwl["q"]), torch.empty_like(gwl["k"]))
+            gwl["fwd"] = lambda: plan.forward(gwl["q"], gwl["k"], out=gattn)
+            gwl["bwd"] = lambda: plan.backward(gwl["g"], gwl["q"], gwl["k"], out=gout)
+            t = time_steps(torch, gwl, args.steps, args.warmup, sync_all)
+            ms = shard.max_over_ranks(t["total_ms"], dev) / args.steps
+            out["grid"] = {"value": units / (ms * 1e-3) / 1e9, "unit": unit, "ms_per_step": ms,
+                           "fwd_ms": shard.max_over_ranks(t["fwd_ms"], dev), "bwd_ms": shard.max_over_ranks(t["bwd_ms"], dev),
+                           "partition": "square blocks: " + plan.describe(), "collective": plan.collective_note()}
+            del gwl, gattn, gout
         b0, b1, h0, h1 = shard.dense_partition(bs, h, world)[rank]
         swl = setup_dense(torch, cabi, (b1 - b0, n, h1 - h0, w), dev, 2000 + rank)
         t = time_steps(torch, swl, args.steps, args.warmup, sync_all)
         ms = shard.max_over_ranks(t["total_ms"], dev) / args.steps
-        units = float(bs) * h * n * n * w
-        return {"value": units / (ms * 1e-3) / 1e9, "unit": unit, "ms_per_step": ms, "collective": None,
-                "partition": "(batch, head group): rank 0 holds batch %d..%d, heads %d..%d of %s; outputs stay on their rank"
-                             % (b0, b1, h0, h1, list(shape))}
+        out.update({"value": units / (ms * 1e-3) / 1e9, "unit": unit, "ms_per_step": ms, "collective": None,
+                    "partition": "(batch, head group): rank 0 holds batch %d..%d, heads %d..%d of %s; outputs stay on their rank"
+                                 % (b0, b1, h0, h1, list(shape))})
+        if "grid" in out and out["grid"]["value"] > out["value"]:  # report the better partition as the strong-scaling figure
+            out = dict(out["grid"], head_groups={k: out[k] for k in ("value", "ms_per_step", "partition")})
+        return out
     import l1attn_sparse_cuda
     co = bench_graph(n, wl["fan"], 4001)
     plan = shard.SparseShard(co, bs, n, rank, world, device=dev)

@@ -11,6 +11,10 @@ outputs is only needed if one rank wants everything.
   dense_partition(bs, heads, world)  (batch, head group) slab of every rank for the dense operator
   dense_local(t, slab)               a rank's contiguous [b0:b1, :, h0:h1, :] copy of q or k
   gather_dense(local, bs, heads)     all-gather of the [B_loc, T, T, H_loc] score slabs into [B, T, T, H]
+  dense_grid_partition(...)          (batch, head group, query block, key block) of every rank: for fewer batch
+                                     items than ranks, the ranks of one item tile its T x T scores with squares
+  DenseGridShard                     the dense operator on that partition: square single-GPU calls, then ONE
+                                     all-reduce each of d_q (over the ranks that share the query block) and d_k
   SparseShard                        the sparse operator over the ranks: by batch item when there are at
                                      least as many items as ranks, else by dst-token range with ONE
                                      all-reduce of the d_k and d_v partial sums
@@ -100,6 +104,143 @@ def gather_dense(local, bs, n_heads):
     for p, (b0, b1, h0, h1) in zip(parts, part):
         full[b0:b1, :, :, h0:h1] = p[: b1 - b0, :, :, : h1 - h0]
     return full
+
+
+# ------------------------------------------------------------------ dense: square blocks of the scores of one item
+
+def _grid_shape(n_ranks, n_heads, n_tok, lane_heads=8):
+    """(head groups, g) with head groups x g x g == n_ranks: the ranks of one batch item tile its scores with
+    g x g square blocks per head group; g = 1 is the plain head-group split.  Chosen for the fullest lanes: the
+    forward's work item is `lane_heads` heads wide, so a rank with 2 heads runs it at a quarter of its rate;
+    among equals the smallest g (least to exchange).  g must divide n_tok so that the blocks are square."""
+    def fill(hs):
+        h = -(-n_heads // hs)  # the widest group
+        return h / float(lane_heads * -(-h // lane_heads))
+    best, best_fill = (n_ranks, 1), fill(n_ranks) if n_ranks <= n_heads else -1.0
+    for g in range(2, int(n_ranks ** 0.5) + 1):
+        if n_ranks % (g * g) or n_tok % g:
+            continue
+        hs = n_ranks // (g * g)
+        if hs <= n_heads and fill(hs) > best_fill + 1e-9:
+            best, best_fill = (hs, g), fill(hs)
+    return best
+
+
+def dense_grid_partition(bs, n_heads, n_tok, world, lane_heads=8):
+    """Per rank a dict(b0, b1, h0, h1, t0, t1, s0, s1, row, col): batch items, heads, query rows (t) and key rows
+    (s) of its block of the scores attn[b, s, t, h]; `row` lists the ranks that hold the same (b, heads, query
+    block) -- their d_q partial sums add up -- and `col` those with the same (b, heads, key block), for d_k.
+    With at least as many batch items as ranks this is dense_partition(): whole items, no exchange.  Otherwise
+    the ranks of one item form head groups x (g x g) square blocks, every block a square problem of n_tok / g
+    tokens for the single-GPU operator.  Against splitting the heads further this keeps the head groups wide
+    enough for the kernels (a rank with 2 heads runs the forward at a quarter of its rate) at the price of two
+    small all-reduces in the backward."""
+    if bs >= world:
+        return [dict(b0=b0, b1=b1, h0=h0, h1=h1, t0=0, t1=n_tok, s0=0, s1=n_tok, row=[r], col=[r])
+                for r, (b0, b1, h0, h1) in enumerate(dense_partition(bs, n_heads, world))]
+    if bs <= 0 or n_heads <= 0 or world <= 0 or n_tok <= 0:
+        raise ValueError("bad partition request bs=%r heads=%r n_tok=%r world=%r" % (bs, n_heads, n_tok, world))
+    out = []
+    for b in range(bs):
+        r0, r1 = shard_range(world, b, bs)
+        hs, g = _grid_shape(r1 - r0, n_heads, n_tok, lane_heads)
+        if hs > n_heads:
+            raise ValueError("%d ranks for one batch item but only %d heads" % (r1 - r0, n_heads))
+        for j in range(hs):
+            h0, h1 = shard_range(n_heads, j, hs)
+            base = r0 + j * g * g
+            for ti in range(g):
+                for si in range(g):
+                    t0, t1 = shard_range(n_tok, ti, g)
+                    s0, s1 = shard_range(n_tok, si, g)
+                    out.append(dict(b0=b, b1=b + 1, h0=h0, h1=h1, t0=t0, t1=t1, s0=s0, s1=s1,
+                                    row=[base + ti * g + x for x in range(g)],
+                                    col=[base + x * g + si for x in range(g)]))
+    return out
+
+
+def _cuda_dense_ops():
+    import l1attn_cabi as cabi
+
+    class Ops:
+        def forward(self, q, k, out):
+            return cabi.dense_fwd(q, k, out=out)
+
+        def backward(self, d_attn, q, k, out, scratch):
+            return cabi.dense_bwd(d_attn, q, k, out=out, scratch=scratch if scratch is not None else "auto")
+
+        def scratch(self, q):
+            import torch as _t
+            n = cabi.lib().l1attn_dense_bwd_scratch_bytes(q.shape[0], q.shape[1], q.shape[2], q.shape[3], cabi._tdt(q))
+            return _t.empty(max(int(n), 1), dtype=_t.uint8, device=q.device)
+    return Ops()
+
+
+class DenseGridShard:
+    """L1Attn forward + backward of ONE global problem [bs, n_tok, n_heads, width] over `world` ranks.
+
+    Every rank runs the single-GPU operator on a square block: queries q[b, t0:t1, h0:h1], keys k[b, s0:s1, h0:h1]
+    -> scores attn[b, s0:s1, t0:t1, h0:h1], which stay on the rank.  In the backward the rank's d_q covers its
+    query rows but only the keys of its block, and its d_k its key rows but only its queries: ONE all-reduce of
+    d_q over the ranks of the same query block and ONE of d_k over those of the same key block complete them
+    (none when a rank holds whole batch items).  All ranks must construct this object at the same point: it
+    creates the process groups.  No kernel reads another GPU's memory; the sums go through torch.distributed.
+
+    `ops` is the compute backend (default: this library; the CPU tests of the partition logic pass a stand-in)."""
+
+    def __init__(self, bs, n_tok, n_heads, rank, world, ops=None, lane_heads=8):
+        self.part = dense_grid_partition(bs, n_heads, n_tok, world, lane_heads)
+        self.me = self.part[rank]
+        self.rank, self.world = rank, world
+        self.ops = ops if ops is not None else _cuda_dense_ops()
+        self.row_group = self.col_group = None
+        # every rank creates every group, in the same order (new_group is collective over the whole job)
+        seen = {}
+        if world > 1 and dist.is_available() and dist.is_initialized():
+            for p in self.part:
+                for key in (tuple(p["row"]), tuple(p["col"])):
+                    if len(key) > 1 and key not in seen:
+                        seen[key] = dist.new_group(list(key))
+            self.row_group = seen.get(tuple(self.me["row"]))
+            self.col_group = seen.get(tuple(self.me["col"]))
+        self._scratch = None
+
+    def local_inputs(self, q, k):
+        """The rank's contiguous blocks of the global q and k."""
+        m = self.me
+        return (q[m["b0"]:m["b1"], m["t0"]:m["t1"], m["h0"]:m["h1"]].contiguous(),
+                k[m["b0"]:m["b1"], m["s0"]:m["s1"], m["h0"]:m["h1"]].contiguous())
+
+    def local_scores(self, attn):
+        """The rank's block of a global [bs, n_tok, n_tok, n_heads] tensor in the layout of the scores."""
+        m = self.me
+        return attn[m["b0"]:m["b1"], m["s0"]:m["s1"], m["t0"]:m["t1"], m["h0"]:m["h1"]].contiguous()
+
+    def forward(self, q_loc, k_loc, out=None):
+        return self.ops.forward(q_loc, k_loc, out)
+
+    def backward(self, d_attn_loc, q_loc, k_loc, out=None):
+        """Returns (d_q of the rank's query rows, d_k of its key rows), complete after the two all-reduces."""
+        if self._scratch is None or self._scratch_for != tuple(q_loc.shape):
+            self._scratch = self.ops.scratch(q_loc)
+            self._scratch_for = tuple(q_loc.shape)
+        d_q, d_k = self.ops.backward(d_attn_loc, q_loc, k_loc, out, self._scratch)
+        if self.row_group is not None:
+            dist.all_reduce(d_q, group=self.row_group)
+        if self.col_group is not None:
+            dist.all_reduce(d_k, group=self.col_group)
+        return d_q, d_k
+
+    def describe(self):
+        m = self.me
+        return ("rank %d: batch %d..%d, heads %d..%d, query rows %d..%d, key rows %d..%d"
+                % (self.rank, m["b0"], m["b1"], m["h0"], m["h1"], m["t0"], m["t1"], m["s0"], m["s1"]))
+
+    def collective_note(self):
+        m = self.me
+        if len(m["row"]) == 1 and len(m["col"]) == 1:
+            return None
+        return ("all_reduce(SUM) of d_q over ranks %s and of d_k over ranks %s" % (m["row"], m["col"]))
 
 
 # ------------------------------------------------------------------ sparse: batch items or dst-token ranges

@@ -1,5 +1,6 @@
 """Multi-process (world_size 2 and 3, gloo, CPU) tests of the partitioning used for N > 1 GPUs: batch slices,
-(batch, head group) slabs of the dense operator, and the sparse operator by dst-token range with its one
+(batch, head group) slabs of the dense operator, square blocks of one item's scores with the two all-reduces of the
+d_q / d_k partial sums, and the sparse operator by dst-token range with its one
 all-reduce of the d_k / d_v partial sums.  The compute itself is a pure-torch stand-in here (the library has no
 CPU path); what is tested is the partition, the placement of the pieces and the collectives."""
 import os
@@ -117,6 +118,93 @@ def test_head_group_shards_assemble_to_the_global_scores(world, shape):
         p.join(timeout=60)
         assert p.exitcode == 0
     assert all(ok for _, ok in res)
+
+
+# ------------------------------------------------------------------ square blocks of one item's scores
+
+def test_grid_partition_tiles_every_score_once_and_names_the_right_partners():
+    sys.path.insert(0, PKG)
+    import l1attn_shard as sh
+    for bs, heads, n, world in [(2, 8, 4096, 8), (1, 16, 64, 8), (1, 8, 32, 8), (1, 4, 6, 4), (2, 8, 16, 4), (3, 5, 10, 7),
+                                (16, 16, 8, 8), (1, 32, 12, 16), (1, 8, 7, 4)]:
+        part = sh.dense_grid_partition(bs, heads, n, world)
+        assert len(part) == world
+        seen = torch.zeros(bs, n, n, heads, dtype=torch.int32)
+        for r, p in enumerate(part):
+            assert p["t1"] - p["t0"] == p["s1"] - p["s0"], "blocks must be square problems"
+            seen[p["b0"]:p["b1"], p["s0"]:p["s1"], p["t0"]:p["t1"], p["h0"]:p["h1"]] += 1
+            assert r in p["row"] and r in p["col"]
+            same = lambda a, b, keys: all(a[x] == b[x] for x in keys)
+            for o, po in enumerate(part):  # partners: exactly the ranks with the same (b, heads, query / key block)
+                assert (o in p["row"]) == same(p, po, ("b0", "b1", "h0", "h1", "t0", "t1"))
+                assert (o in p["col"]) == same(p, po, ("b0", "b1", "h0", "h1", "s0", "s1"))
+        assert bool((seen == 1).all()), (bs, heads, n, world)
+    cfg3 = sh.dense_grid_partition(2, 8, 4096, 8)  # long-context shape on 8 ranks: all heads, 2 x 2 blocks per item
+    assert [cfg3[5][x] for x in ("b0", "h0", "h1", "t0", "t1", "s0", "s1")] == [1, 0, 8, 0, 2048, 2048, 4096]
+    assert cfg3[5]["row"] == [4, 5] and cfg3[5]["col"] == [5, 7]
+    odd = sh.dense_grid_partition(1, 8, 7, 4)      # 7 tokens cannot be halved: plain head groups
+    assert all(p["t1"] - p["t0"] == 7 and p["h1"] - p["h0"] == 2 for p in odd)
+    with pytest.raises(ValueError):
+        sh.dense_grid_partition(1, 2, 9, 3)
+
+
+class _TorchDenseOps:
+    """Stand-in for the single-GPU dense operator on the CPU (differentiable torch)."""
+
+    def forward(self, q, k, out):
+        return _torch_scores(q, k)
+
+    def backward(self, d_attn, q, k, out, scratch):
+        q, k = q.detach().clone().requires_grad_(True), k.detach().clone().requires_grad_(True)
+        _torch_scores(q, k).backward(d_attn)
+        return q.grad, k.grad
+
+    def scratch(self, q):
+        return None
+
+
+def _grid_worker(rank, world, port, shape, q):
+    sys.path.insert(0, PKG)
+    import l1attn_shard as sh
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        bs, n, h, w = shape
+        g = torch.Generator().manual_seed(7)
+        qq, kk = (torch.randn(shape, generator=g, dtype=torch.float64) for _ in range(2))
+        d_attn = torch.randn(bs, n, n, h, generator=g, dtype=torch.float64)
+        ops = _TorchDenseOps()
+        plan = sh.DenseGridShard(bs, n, h, rank, world, ops=ops)
+        ql, kl = plan.local_inputs(qq, kk)
+        attn = plan.forward(ql, kl)
+        dq, dk = plan.backward(plan.local_scores(d_attn), ql, kl)
+        ref = _torch_scores(qq, kk)
+        rdq, rdk = ops.backward(d_attn, qq, kk, None, None)
+        m = plan.me
+        close = lambda a, b: bool(torch.allclose(a, b, rtol=1e-12, atol=1e-12))
+        ok = (close(attn, plan.local_scores(ref))
+              and close(dq, rdq[m["b0"]:m["b1"], m["t0"]:m["t1"], m["h0"]:m["h1"]])
+              and close(dk, rdk[m["b0"]:m["b1"], m["s0"]:m["s1"], m["h0"]:m["h1"]]))
+        q.put((rank, ok, plan.collective_note() is not None, plan.describe()))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,shape,exchange", [(4, (1, 6, 4, 3), True), (2, (1, 6, 4, 3), False), (3, (4, 5, 2, 3), False)])
+def test_square_block_shards_give_the_global_gradients(world, shape, exchange):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 35500 + (os.getpid() * 17 + world * 23 + shape[0]) % 2000
+    procs = [ctx.Process(target=_grid_worker, args=(r, world, port, shape, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = sorted(q.get(timeout=120) for _ in range(world))
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert all(ok for _, ok, _, _ in res), res
+    assert all(ex == exchange for _, _, ex, _ in res), res
 
 
 # ------------------------------------------------------------------ sparse by dst-token range
