@@ -859,24 +859,30 @@ def run_strong(torch, dist, cabi, shard, args, wl, rank, world, dev, sync_all):
         return out
     import l1attn_sparse_cuda
     co = bench_graph(n, wl["fan"], 4001)
-    plan = shard.SparseShard(co, bs, n, rank, world, device=dev)
     gen = torch.Generator(device=dev).manual_seed(4100)  # same tensors on every rank (replicated inputs)
     q, k = (args.qk_scale * torch.randn(shape, generator=gen, device=dev) for _ in range(2))
     v, dvo = (torch.randn(shape, generator=gen, device=dev) for _ in range(2))
-    step = lambda: plan.forward_backward(v, q, k, dvo, True)
-    for _ in range(max(args.warmup, 3)):
-        step()
-    sync_all()
-    e0, e1 = _events(torch, 2)
-    e0.record()
-    for _ in range(args.steps):
-        step()
-    e1.record()
-    sync_all()
-    ms = shard.max_over_ranks(e0.elapsed_time(e1), dev) / args.steps
     units = float(co.shape[0]) * bs * h
-    return {"value": units / (ms * 1e-3) / 1e9, "unit": unit, "ms_per_step": ms, "partition": plan.describe(),
-            "collective": plan.collective_note()}
+
+    def run(mode):
+        plan = shard.SparseShard(co, bs, n, rank, world, device=dev, n_heads=h, mode=mode)
+        step = lambda: plan.forward_backward(v, q, k, dvo, True)
+        for _ in range(max(args.warmup, 3)):
+            step()
+        sync_all()
+        e0, e1 = _events(torch, 2)
+        e0.record()
+        for _ in range(args.steps):
+            step()
+        e1.record()
+        sync_all()
+        ms = shard.max_over_ranks(e0.elapsed_time(e1), dev) / args.steps
+        return {"value": units / (ms * 1e-3) / 1e9, "unit": unit, "ms_per_step": ms, "partition": plan.describe(),
+                "collective": plan.collective_note()}
+    out = run("auto")
+    if bs < world:  # also the dst-token-range form with its all-reduce, whichever form "auto" chose
+        out["dst_range"] = run("dst")
+    return out
 
 
 def main():

@@ -209,7 +209,6 @@ dense_bwd_sv_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_const
 	auto transpose_row = [&](unsigned m) {
 		const int st = int(m & 1u);
 		if (m < n_tiles) {
-#ifndef SV_EXP_NO_TRANSPOSE
 			if (sv_opaque(dead) == 0 && !mbar_wait(&bars.raw_full[st], (m >> 1) & 1u, err))
 				dead = 1;
 			const float4 *R = reinterpret_cast<const float4 *>(raw + st * SV_RAW_BYTES) + warp * SV_TX;
@@ -244,7 +243,6 @@ dense_bwd_sv_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_const
 			kc += __shfl_xor_sync(0xffffffffu, kc, 1);
 			if ((ln & 7) == 0) // lanes 0, 8, 16, 24 hold heads 0, 1, 2, 3
 				csring[(m & 3u) * (SV_TY * SV_HG) + warp * SV_HG + (ln >> 3)] = kc; // read two steps later: four slots keep writer and reader apart
-#endif
 		}
 		__syncwarp();
 		if (sv_opaque(lane) == 0)
@@ -311,10 +309,8 @@ dense_bwd_sv_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_const
 				issue_kb();  // k rows of tile n + 1 into the stage the math of tile n - 1 has left
 			}
 			sv_tile_compute(gts + st * SV_GTSTAGE, pkbase + st * (SV_PK_BYTES / 4) + warp * (SV_TY * 32) + lane, xg, h, lane, a, acc, rsq);
-#ifndef SV_EXP_NO_REDUCE
 			if (sv_opaque(red_s0) >= 0)
 				reduce_prev(n - 1u);
-#endif
 			red_pp = item_pp;
 			red_s0 = tile * SV_TY;
 			red_rows = sv_opaque(item_ok) != 0 ? n_tok - red_s0 : 0;

@@ -94,7 +94,7 @@ dense_fwd_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_cons
 			for (unsigned item = blockIdx.x; item < wk.total; item += gridDim.x) {
 				const Item x = decode_item(wk, item);
 				for (int ci = 0; ci < nchunk; ci++) {
-					if (!mbar_wait(&empty_bar[st], ph, err))
+					if (!mbar_wait_relaxed(&empty_bar[st], ph, err))
 						return;
 					unsigned char *dst = stages + size_t(st) * STAGE_BYTES;
 					mbar_expect_tx(&full_bar[st], STAGE_BYTES);

@@ -696,12 +696,40 @@ __global__ void __launch_bounds__(256) sparse_bwd_src_kernel(SparseArgs a, const
 	}
 }
 
+// Lanes per head.  Four 16-byte vectors per lane is the fastest walk (fewer shuffle rounds, less index math per
+// term), but a warp then covers 32 / lph heads, and with fewer heads than that (a head-group shard of a multi-GPU
+// run, a model with few heads) the other lanes idle.  `idle_den`: more lanes share a head when at least
+// (idle_den - 1) / idle_den of them would idle otherwise.  Measured at 4096 tokens, 131072 edges, width 64, one batch item:
+// forward 4 heads 0.038 ms against 0.055 ms, 2 heads 0.030 / 0.050; backward 4 heads 0.124 against 0.107 (the
+// unrolled four-vector walk wins although half its lanes idle), 2 heads 0.073 / 0.104 -- so the forward asks
+// with idle_den 2 and the backward with 4.
+int lanes_per_head(int mw, int n_heads, int vec, int idle_den);
 int pow2_ceil(int x)
 {
 	int p = 1;
 	while (p < x)
 		p <<= 1;
 	return p;
+}
+
+int lanes_per_head(int mw, int n_heads, int vec, int idle_den)
+{
+	int lph = pow2_ceil((mw + 4 * vec - 1) / (4 * vec));
+	if (lph > 32)
+		lph = 32;
+	{
+		const int hpw = 32 / lph, slots = hpw * ((n_heads + hpw - 1) / hpw);
+		if (idle_den * (slots - n_heads) < (idle_den - 1) * slots)
+			return lph; // few enough idle lanes as it is
+	}
+	static const bool no_fill = getenv("L1ATTN_SPARSE_NO_FILL") != nullptr; // debugging aid: keep four vectors per lane
+	while (!no_fill && lph < 32 && mw >= 2 * lph * vec) {
+		const int hpw = 32 / lph, slots = hpw * ((n_heads + hpw - 1) / hpw);
+		if (2 * n_heads > slots)
+			break; // more than half the lanes busy
+		lph *= 2;
+	}
+	return lph;
 }
 
 struct Grid {
@@ -720,9 +748,7 @@ template <typename S, typename T, int VEC>
 int fwd_t(SparseArgs a, const S *v, const S *vb, const S *q, const S *k, S *vo, S *attn, cudaStream_t st)
 {
 	const int mw = a.width > a.v_width ? a.width : a.v_width;
-	a.lph = pow2_ceil((mw + 4 * VEC - 1) / (4 * VEC)); // four 16-byte vectors per lane: fewer shuffle rounds and less index math per term
-	if (a.lph > 32)
-		a.lph = 32;
+	a.lph = lanes_per_head(mw, a.n_heads, VEC, 2);
 	const Grid g = grid_for(a);
 	if (!g.ok)
 		return L1ATTN_ERR_SHAPE;
@@ -766,11 +792,8 @@ int bwd_t(SparseArgs a, const T *dvo, const T *v, const T *vb, const T *q, const
 	  T *d_vb, T *d_q, T *d_k, T *dx, cudaStream_t st)
 {
 	const int mw = a.width > a.v_width ? a.width : a.v_width;
-	// four 16-byte vectors per lane: fewer shuffle rounds and less index math per term (two per lane, twice the
-	// warps at ~75 registers, measured 2 % slower)
-	a.lph = pow2_ceil((mw + 4 * VEC - 1) / (4 * VEC));
-	if (a.lph > 32)
-		a.lph = 32;
+	// (two vectors per lane, twice the warps at ~75 registers, measured 2 % slower than four at 8 heads)
+	a.lph = lanes_per_head(mw, a.n_heads, VEC, 4);
 	const Grid g = grid_for(a);
 	if (!g.ok)
 		return L1ATTN_ERR_SHAPE;

@@ -271,25 +271,43 @@ class SparseShard:
     """L1AttnSparse forward + backward over `world` ranks.
 
     mode "batch"  (bs >= world): rank r owns batch items shard_range(bs, r, world); nothing is exchanged.
-    mode "dst"    (bs <  world): every rank keeps q, k, v (replicated) and owns the dst tokens
+    mode "head"   (bs <  world, and no more ranks per item than heads): the operator is independent per (batch item,
+                  head) too, so the ranks of one item split its heads (dense_partition); every rank works on
+                  contiguous [B_loc, n, H_loc, W] copies of q, k, v with the full graph; nothing is exchanged.
+    mode "dst"    (what is left, or on request): every rank keeps q, k, v (replicated) and owns the dst tokens
                   shard_range(n_tok, r, world): it runs the operator on the sub-list of edges whose dst it
                   owns.  All edges of a dst stay together and keep their order, so their softmax slots are
                   those of the full list; vo, attn and d_q rows of the owned tokens are complete (other rows
                   are zero).  d_k and d_v scatter to arbitrary src tokens, so each rank holds partial sums:
-                  they are written into ONE flat buffer and summed with ONE all-reduce.
+                  they are written into ONE flat buffer and summed with ONE all-reduce.  That all-reduce moves
+                  as many bytes as d_k and d_v have, whatever the rank count, so this mode pays only where the
+                  kernels take much longer than it.
 
-    `ops` is the compute backend (default: this library on `device`; there is no CPU implementation --
+    `mode` = "auto" picks the first of these that applies.  `n_heads` is needed for "head" (without it "auto" skips
+    that mode).  `ops` is the compute backend (default: this library on `device`; there is no CPU implementation --
     the CPU tests of the partition logic pass a stand-in)."""
 
-    def __init__(self, co, bs, n_tok, rank, world, device="cuda", ops=None):
+    def __init__(self, co, bs, n_tok, rank, world, device="cuda", ops=None, n_heads=None, mode="auto"):
         self.bs, self.n_tok, self.rank, self.world, self.device = bs, n_tok, rank, world, device
         self.ops = ops if ops is not None else _cuda_sparse_ops(device)
         co = torch.as_tensor(co)
-        self.mode = "batch" if bs >= world else "dst"
-        if self.mode == "batch":
+        if mode not in ("auto", "batch", "head", "dst"):
+            raise ValueError("unknown mode %r" % (mode,))
+        if mode == "auto":
+            ranks_per_item = -(-world // max(bs, 1))
+            mode = "batch" if bs >= world else ("head" if n_heads is not None and ranks_per_item <= n_heads else "dst")
+        if mode == "batch" and bs < world:
+            raise ValueError("batch mode needs at least as many batch items (%d) as ranks (%d)" % (bs, world))
+        self.mode = mode
+        self.h0, self.h1 = 0, n_heads
+        self.d0, self.d1 = 0, n_tok
+        mine = co
+        if mode == "batch":
             self.b0, self.b1 = shard_range(bs, rank, world)
-            self.d0, self.d1 = 0, n_tok
-            mine = co
+        elif mode == "head":
+            if n_heads is None:
+                raise ValueError("head mode needs n_heads")
+            self.b0, self.b1, self.h0, self.h1 = dense_partition(bs, n_heads, world)[rank]
         else:
             self.b0, self.b1 = 0, bs
             self.d0, self.d1 = shard_range(n_tok, rank, world)
@@ -302,19 +320,26 @@ class SparseShard:
     def describe(self):
         if self.mode == "batch":
             return "batch items %d..%d of %d on rank %d, full graph, no collective" % (self.b0, self.b1, self.bs, self.rank)
+        if self.mode == "head":
+            return ("batch items %d..%d, heads %d..%d on rank %d, full graph, no collective"
+                    % (self.b0, self.b1, self.h0, self.h1, self.rank))
         return ("dst tokens %d..%d of %d on rank %d (%d of %d edges), q, k, v replicated"
                 % (self.d0, self.d1, self.n_tok, self.rank, self.n_edges_local, self.n_edges))
 
     def collective_note(self):
-        if self.mode == "batch" or self._buf is None:
+        if self.mode != "dst" or self._buf is None:
             return None
         return "one all_reduce(SUM) of d_k and d_v in one buffer: %d bytes per rank" % (self._buf.numel() * self._buf.element_size())
 
     def forward_backward(self, v, q, k, dvo, use_softmax=True):
-        """Returns (vo, d_v, d_q, d_k).  batch mode: the rank's batch slice of each.  dst mode: vo and d_q hold
-        the owned dst rows (zero elsewhere); d_v and d_k are complete on every rank after the all-reduce."""
+        """Returns (vo, d_v, d_q, d_k).  batch mode: the rank's batch slice of each; head mode: its (batch, head)
+        slab.  dst mode: vo and d_q hold the owned dst rows (zero elsewhere); d_v and d_k are complete on every
+        rank after the all-reduce."""
         sl = slice(self.b0, self.b1)
-        v, q, k, dvo = v[sl], q[sl], k[sl], dvo[sl]
+        if self.mode == "head":
+            v, q, k, dvo = (t[sl, :, self.h0:self.h1].contiguous() for t in (v, q, k, dvo))
+        else:
+            v, q, k, dvo = v[sl], q[sl], k[sl], dvo[sl]
         bs, n, h, w = q.shape
         wv = v.shape[3]
         if self._buf is None or self._buf.dtype != q.dtype or self._buf.numel() != k.numel() + v.numel():

@@ -243,7 +243,7 @@ class _TorchSparseOps:
             o.copy_(t.grad if t.grad is not None else torch.zeros_like(t))
 
 
-def _sparse_worker(rank, world, port, bs, q):
+def _sparse_worker(rank, world, port, bs, mode, q):
     sys.path.insert(0, PKG)
     import l1attn_shard as sh
     os.environ["MASTER_ADDR"] = "127.0.0.1"
@@ -255,14 +255,15 @@ def _sparse_worker(rank, world, port, bs, q):
         co = torch.stack([torch.randint(0, n, (60,), generator=g), torch.randint(0, n, (60,), generator=g)], 1)
         v, qq, kk, dvo = (torch.randn(bs, n, h, w, generator=g, dtype=torch.float64) for _ in range(4))
         ops = _TorchSparseOps()
-        plan = sh.SparseShard(co, bs, n, rank, world, device="cpu", ops=ops)
+        plan = sh.SparseShard(co, bs, n, rank, world, device="cpu", ops=ops, n_heads=h, mode=mode)
         vo, dv, dq, dk = plan.forward_backward(v, qq, kk, dvo, True)
         whole = sh.SparseShard(co, bs, n, 0, 1, device="cpu", ops=ops)
         rvo, rdv, rdq, rdk = whole.forward_backward(v, qq, kk, dvo, True)
         close = lambda a, b: bool(torch.allclose(a, b, rtol=1e-12, atol=1e-12))
-        if plan.mode == "batch":
-            sl = slice(plan.b0, plan.b1)
+        if plan.mode in ("batch", "head"):
+            sl = (slice(plan.b0, plan.b1), slice(None), slice(plan.h0, plan.h1))
             ok = close(vo, rvo[sl]) and close(dv, rdv[sl]) and close(dq, rdq[sl]) and close(dk, rdk[sl])
+            ok = ok and plan.collective_note() is None
         else:
             rows = slice(plan.d0, plan.d1)
             outside = torch.ones(n, dtype=torch.bool)
@@ -276,12 +277,13 @@ def _sparse_worker(rank, world, port, bs, q):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world,bs", [(2, 1), (3, 2), (2, 4)])
-def test_sparse_dst_range_and_batch_shards(world, bs):
+@pytest.mark.parametrize("world,bs,mode,want", [(2, 1, "dst", "dst"), (3, 2, "dst", "dst"), (2, 4, "auto", "batch"),
+                                                (2, 1, "auto", "head"), (3, 2, "auto", "head")])
+def test_sparse_dst_range_head_and_batch_shards(world, bs, mode, want):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    port = 33500 + (os.getpid() * 13 + world * 19 + bs) % 2000
-    procs = [ctx.Process(target=_sparse_worker, args=(r, world, port, bs, q)) for r in range(world)]
+    port = 33500 + (os.getpid() * 13 + world * 19 + bs + 7 * len(mode)) % 2000
+    procs = [ctx.Process(target=_sparse_worker, args=(r, world, port, bs, mode, q)) for r in range(world)]
     for p in procs:
         p.start()
     res = sorted(q.get(timeout=120) for _ in range(world))
@@ -289,6 +291,6 @@ def test_sparse_dst_range_and_batch_shards(world, bs):
         p.join(timeout=60)
         assert p.exitcode == 0
     assert all(ok for _, _, ok, _ in res), res
-    assert {m for _, m, _, _ in res} == ({"batch"} if bs >= world else {"dst"})
-    if bs < world:
+    assert {m for _, m, _, _ in res} == {want}
+    if want == "dst":
         assert sum(e for _, _, _, e in res) == 60  # every edge on exactly one rank
