@@ -29,16 +29,18 @@
 namespace l1b {
 namespace {
 
-constexpr int HG = 8;       // heads per work item
-constexpr int LT = 4;       // lanes along the query axis
+// A work item is HG heads x TT query rows x TS key rows with HG * TT = 512: HG = 8 (TT = 64) or, for head counts
+// that leave fewer idle lanes in groups of four (4, 12, 20 ... heads; a head-group shard of a multi-GPU run),
+// HG = 4 (TT = 128).  The lanes of a warp are the 32 consecutive (query row, head) rows of the q tile either way.
 constexpr int CH = 4;       // 16-byte chunks per (token, head) row per stage
 constexpr int NCW = 8;      // compute warps: 2 (query halves) x 4 (key groups)
 constexpr int NSTAGE = 3;
-constexpr int TT = 64, TS = 32;
+constexpr int TS = 32;
 constexpr int TM = 8, TN = 8;
-constexpr int Q_BYTES = TT * HG * CH * 16, K_BYTES = TS * HG * CH * 16;
-constexpr int STAGE_BYTES = Q_BYTES + K_BYTES; // 49152
-constexpr int OUT_BYTES = TS * TT * HG * 4;      // 65536: staging tile [s][t][h] of the TMA store
+constexpr int Q_BYTES = 512 * CH * 16;           // 32768: TT * HG rows of 64 bytes
+constexpr int K_BYTES_MAX = TS * 8 * CH * 16;    // 16384 (HG = 8; half of it with HG = 4)
+constexpr int STAGE_BYTES = Q_BYTES + K_BYTES_MAX; // 49152
+constexpr int OUT_BYTES = TS * 512 * 4;          // 65536: staging tile [s][t][h] of the TMA store
 constexpr int NTHREADS = (NCW + 1) * 32;
 
 struct Work {
@@ -48,8 +50,9 @@ struct Work {
 struct Item {
 	int t0, s0, h0, b;
 };
-__device__ __forceinline__ Item decode_item(const Work &wk, unsigned r)
+template <int HG> __device__ __forceinline__ Item decode_item(const Work &wk, unsigned r)
 {
+	constexpr int TT = 512 / HG;
 	Item x;
 	x.t0 = int(r % wk.ntt) * TT;
 	r /= wk.ntt;
@@ -60,14 +63,15 @@ __device__ __forceinline__ Item decode_item(const Work &wk, unsigned r)
 	return x;
 }
 
-template <typename T> // instantiated for float only: the packed subtract below is fp32
+template <typename T, int HG> // instantiated for float only: the packed subtract below is fp32
 __global__ void __launch_bounds__(NTHREADS, 1)
 dense_fwd_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kmap,
 		     const __grid_constant__ CUtensorMap omap, int tma_store, T *__restrict__ attn, int n_tok, int n_heads, int width, T scale, Work wk, int *err)
 {
 	constexpr int VEC = 16 / sizeof(T);
 	constexpr int WC = CH * VEC;
-	using V = Pack<T, VEC>;
+	constexpr int LT = 32 / HG;  // lanes along the query axis
+	constexpr int TT = 512 / HG; // query rows per item
 	extern __shared__ __align__(1024) unsigned char smem_raw[];
 	// 1024-byte alignment by OFFSET into the shared array: a pointer rebuilt from an integer loses its
 	// address space and every access through it becomes a generic load, which measured ~2x slower here
@@ -92,12 +96,12 @@ dense_fwd_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_cons
 			int st = 0;
 			uint32_t ph = 1; // a fresh barrier reads as "previous phase (parity 1) complete"
 			for (unsigned item = blockIdx.x; item < wk.total; item += gridDim.x) {
-				const Item x = decode_item(wk, item);
+				const Item x = decode_item<HG>(wk, item);
 				for (int ci = 0; ci < nchunk; ci++) {
 					if (!mbar_wait_relaxed(&empty_bar[st], ph, err))
 						return;
 					unsigned char *dst = stages + size_t(st) * STAGE_BYTES;
-					mbar_expect_tx(&full_bar[st], STAGE_BYTES);
+					mbar_expect_tx(&full_bar[st], Q_BYTES + TS * HG * CH * 16);
 					tma_load_4d(dst, &qmap, &full_bar[st], ci * WC, x.h0, x.t0, x.b);
 					tma_load_4d(dst + Q_BYTES, &kmap, &full_bar[st], ci * WC, x.h0, x.s0, x.b);
 					if (++st == NSTAGE) {
@@ -111,10 +115,14 @@ dense_fwd_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_cons
 	}
 
 	// ---------------- compute warps
-	const int lane_h = lane & 7, lane_t = lane >> 3;
+	const int lane_h = lane & (HG - 1), lane_t = lane / HG;
 	const int wt = warp & 1, ws = warp >> 1; // 2 query halves x 4 key groups
-	const int sw = (lane_h >> 1) & 3;        // TMA 64-byte swizzle: chunk ^= address bits 7..8 = (head >> 1) & 3
-	const int qoff = ((wt * 32 + lane_t) * HG + lane_h) * CH;
+	// TMA 64-byte swizzle: chunk ^= address bits 7..8 = (row >> 1) & 3, row = token * HG + head within the box.  The
+	// q rows of a warp load are base + lane with base a multiple of 32; the k rows are (ws * TN + j) * HG + head,
+	// where j contributes to those bits only when HG = 4
+	const int sw = (lane >> 1) & 3;
+	const int swk = (lane_h >> 1) & 3;
+	const int qoff = ((wt * (TT / 2) + lane_t) * HG + lane_h) * CH;
 	const int koff = Q_BYTES / 16 + ((ws * TN) * HG + lane_h) * CH;
 	int st = 0;
 	uint32_t ph = 0;
@@ -136,14 +144,14 @@ dense_fwd_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_cons
 			const ulonglong2 *qp = S + qoff, *kp = S + koff;
 #pragma unroll
 			for (int c = 0; c < CH; c++) {
-				const int pc = c ^ sw;
+				const int pc = c ^ sw, pk0 = c ^ swk;
 				// Each 16-byte operand is two register pairs; the subtraction is the packed
 				// sub.f32x2 (one issue slot for two differences), the |.|-accumulation stays
 				// scalar because its abs is a free source modifier only there.
 				ulonglong2 kv[TN];
 #pragma unroll
 				for (int j = 0; j < TN; j++)
-					kv[j] = kp[j * HG * CH + pc];
+					kv[j] = kp[j * HG * CH + (pk0 ^ (HG == 4 ? (2 * j) & 3 : 0))];
 #pragma unroll
 				for (int i = 0; i < TM; i++) {
 					const ulonglong2 qv = qp[i * LT * HG * CH + pc];
@@ -171,13 +179,13 @@ dense_fwd_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_cons
 			}
 		}
 
-		const Item x = decode_item(wk, item);
+		const Item x = decode_item<HG>(wk, item);
 		if (tma_store) {
 			T *stage_out = reinterpret_cast<T *>(stages + size_t(NSTAGE) * STAGE_BYTES);
 			if (tid == 0)
 				tma_store_wait_read(); // the previous item's store has drained the staging tile
 			named_barrier(1, NCW * 32);
-			T *o = stage_out + ((ws * TN) * TT + wt * 32 + lane_t) * HG + lane_h;
+			T *o = stage_out + ((ws * TN) * TT + wt * (TT / 2) + lane_t) * HG + lane_h;
 #pragma unroll
 			for (int j = 0; j < TN; j++)
 #pragma unroll
@@ -202,7 +210,7 @@ dense_fwd_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_cons
 				T *row = ab + size_t(s) * n_tok * n_heads;
 #pragma unroll
 				for (int i = 0; i < TM; i++) {
-					const int t = x.t0 + wt * 32 + lane_t + LT * i;
+					const int t = x.t0 + wt * (TT / 2) + lane_t + LT * i;
 					if (t < n_tok)
 						row[size_t(t) * n_heads] = acc[i][j] * scale;
 				}
@@ -216,10 +224,11 @@ dense_fwd_tma_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_cons
 template <typename T> CUtensorMapDataType tmap_dtype();
 template <> CUtensorMapDataType tmap_dtype<float>() { return CU_TENSOR_MAP_DATA_TYPE_FLOAT32; }
 
-template <typename T>
+template <typename T, int HG>
 int launch(const T *q, const T *k, T *attn, int bs, int n_tok, int n_heads, int width, cudaStream_t st)
 {
 	constexpr int VEC = 16 / sizeof(T);
+	constexpr int TT = 512 / HG;
 	// tensor [bs][n_tok][n_heads][width], innermost first; one stage row is CH*VEC elements = 64 bytes
 	const uint64_t dims[4] = {uint64_t(width), uint64_t(n_heads), uint64_t(n_tok), uint64_t(bs)};
 	const uint64_t strides[3] = {uint64_t(width) * sizeof(T), uint64_t(n_heads) * width * sizeof(T),
@@ -255,7 +264,7 @@ int launch(const T *q, const T *k, T *attn, int bs, int n_tok, int n_heads, int 
 	L1B_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
 	const unsigned grid = wk.total < unsigned(sms) ? wk.total : unsigned(sms);
 	const size_t smem = size_t(NSTAGE) * STAGE_BYTES + OUT_BYTES + 1024;
-	auto kern = dense_fwd_tma_kernel<T>;
+	auto kern = dense_fwd_tma_kernel<T, HG>;
 	L1B_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
 	const T scale = T(-1.0 / sqrt(double(width)));
 	kern<<<unsigned(grid), NTHREADS, smem, st>>>(qmap, kmap, omap, tma_store, attn, n_tok, n_heads, width, scale, wk, err);
@@ -275,7 +284,11 @@ int dense_fwd_tma_launch(const void *q, const void *k, void *attn, int bs, int n
 		return 1;
 	if (dtype != L1ATTN_F32)
 		return 1; // an 8 x 8 tile of doubles does not fit the register file; fp64 uses the generic kernel
-	return launch<float>((const float *)q, (const float *)k, (float *)attn, bs, n_tok, n_heads, width, st);
+	// groups of four heads where they leave fewer lanes idle than groups of eight (4, 12, 20 ... heads)
+	const int idle8 = (n_heads + 7) / 8 * 8 - n_heads, idle4 = (n_heads + 3) / 4 * 4 - n_heads;
+	if (idle4 < idle8)
+		return launch<float, 4>((const float *)q, (const float *)k, (float *)attn, bs, n_tok, n_heads, width, st);
+	return launch<float, 8>((const float *)q, (const float *)k, (float *)attn, bs, n_tok, n_heads, width, st);
 }
 
 } // namespace l1b
