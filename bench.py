@@ -834,6 +834,7 @@ def run_strong(torch, dist, cabi, shard, args, wl, rank, world, dev, sync_all):
             # fewer batch items than ranks: also the square-block partition (all heads of the kernels' work items
             # stay busy; d_q and d_k partial sums meet in one all-reduce each)
             plan = shard.DenseGridShard(bs, n, h, rank, world)
+        if bs < world and any(len(p["row"]) > 1 for p in plan.part):  # (else it is the head-group split below; same answer on every rank)
             m = plan.me
             lshape = (m["b1"] - m["b0"], m["t1"] - m["t0"], m["h1"] - m["h0"], w)
             gwl = setup_dense(torch, cabi, lshape, dev, 2000 + rank)

@@ -76,7 +76,7 @@ int dense_bwd_tma_launch(const void *d_attn, const void *q, const void *k, void 
 			 int n_heads, int width, int dtype, const unsigned char *exact_flags, const int *tie_hdr,
 			 int only_on_overflow, cudaStream_t st);
 int dense_bwd_sv_launch(const void *d_attn, const void *q, const void *k, void *d_q, void *d_k, const int *tie_hdr,
-			void *part, int bs, int n_tok, int n_heads, int width, int dtype, cudaStream_t st);
+			void *part, void *dq_part, int ns, int bs, int n_tok, int n_heads, int width, int dtype, cudaStream_t st);
 // dk_sign: +1 after the two-pass kernel (a tie counted as -scale g in d_k), -1 after the single-visit kernel (+scale g)
 int dense_tiefix_launch(const void *d_attn, void *d_q, void *d_k, const unsigned char *scratch, int bs, int n_tok,
 			int n_heads, int width, int dk_sign, cudaStream_t st);

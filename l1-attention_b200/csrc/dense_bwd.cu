@@ -214,15 +214,15 @@ int dense_bwd_launch(const void *d_attn, const void *q, const void *k, void *d_q
 				int dev = 0, sms = 148;
 				(void)cudaGetDevice(&dev);
 				(void)cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-				auto fill = [&](double items) { return items / (double((long long)((items + sms - 1) / sms)) * sms); };
-				const double it_sv = double(bs) * ((n_heads + 3) / 4) * ((width + 31) / 32) * ((n_tok + 127) / 128);
+				auto fill = [&](double items) { return bwd_wave_fill(items, sms); };
+				const double it_sv = double(bs) * ((n_heads + 3) / 4) * ((width + 31) / 32) * ((n_tok + 127) / 128) * sl.ns;
 				const double it_tp = 2.0 * bs * ((n_heads + 7) / 8) * ((width + 63) / 64) * ((n_tok + 31) / 32);
 				// (and an item of either kernel is only as busy as its head group is full: 4 heads leave half of an
 				// 8-head item's lanes idle)
 				const double hf_sv = double(n_heads) / (4.0 * ((n_heads + 3) / 4)), hf_tp = double(n_heads) / (8.0 * ((n_heads + 7) / 8));
 				if (!no_sv && 1.08 * fill(it_sv) * hf_sv >= fill(it_tp) * hf_tp) {
-					const int frc = dense_bwd_sv_launch(d_attn, q, k, d_q, d_k, tie_hdr, sc + sl.part, bs, n_tok, n_heads, width,
-									    dtype, st);
+					const int frc = dense_bwd_sv_launch(d_attn, q, k, d_q, d_k, tie_hdr, sc + sl.part, sl.ns > 1 ? sc + sl.dqpart : nullptr,
+									    sl.ns, bs, n_tok, n_heads, width, dtype, st);
 					if (frc < 0)
 						return frc;
 					sv = frc == 0;

@@ -51,11 +51,11 @@ static_assert(SV_TX == (SV_NCW / SV_HG) * SV_XR && SV_TY == 4 * (SV_NCW / SV_HG)
 constexpr size_t SV_SMEM = 2 * SV_RAW_BYTES + 2 * SV_GTSTAGE + 2 * SV_PK_BYTES + SV_NCW * 32 * 4 + 4 * SV_CS_BYTES + 1024;
 
 struct SvWork {
-	unsigned nws, ntb, nhg, total;
-	int nt; // tiles of SV_TY source rows per item
+	unsigned nws, ntb, nhg, ns, total;
+	int nt; // tiles of SV_TY source rows per item: those of one of the ns ranges of source rows
 };
 struct SvItem {
-	int b, h0, w0, tb;
+	int b, h0, w0, tb, sh; // sh: which range of source rows
 };
 __device__ __forceinline__ SvItem sv_decode(const SvWork &wk, unsigned r)
 {
@@ -64,6 +64,8 @@ __device__ __forceinline__ SvItem sv_decode(const SvWork &wk, unsigned r)
 	// them at the same time stream the same gradient tiles, so all but the first reader find them in L2
 	it.w0 = int(r % wk.nws) * SV_WS;
 	r /= wk.nws;
+	it.sh = int(r % wk.ns);
+	r /= wk.ns;
 	it.tb = int(r % wk.ntb);
 	r /= wk.ntb;
 	it.h0 = int(r % wk.nhg) * SV_HG;
@@ -136,9 +138,9 @@ __device__ __forceinline__ void sv_tile_compute(const unsigned char *gts, float 
 // overwritten) and with raw slot n & 1 (tile n + 2 may be requested into it).
 __global__ void __launch_bounds__(SV_THREADS, 1)
 dense_bwd_sv_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap gmap,
-		    const float *__restrict__ q, float *__restrict__ d_q, float *__restrict__ part,
+		    const float *__restrict__ q, float *__restrict__ d_q, size_t dq_stride, float *__restrict__ part,
 		    const int *__restrict__ tie_hdr, int bs, int n_tok, int n_heads, int width, float scale, SvWork wk, int *err)
-{
+{ // d_q, dq_stride: the gradient itself and 0, or (source rows split over wk.ns items) the partial sums' buffer and the size of one
 	if (tie_hdr[1] != 0)
 		return; // too many ties to list: the two-pass kernel computes this call
 	extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -188,8 +190,8 @@ dense_bwd_sv_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_const
 			return;
 		const int st = int(cur_raw.m & 1u);
 		mbar_expect_tx(&bars.raw_full[st], SV_RAW_BYTES);
-		tma_load_4d(raw + st * SV_RAW_BYTES, &gmap, &bars.raw_full[st], cur_raw.x.h0, cur_raw.x.tb * SV_TX, cur_raw.tile * SV_TY,
-			    cur_raw.x.b); // box {4 h, 128 t, 16 s}
+		tma_load_4d(raw + st * SV_RAW_BYTES, &gmap, &bars.raw_full[st], cur_raw.x.h0, cur_raw.x.tb * SV_TX,
+			    (cur_raw.x.sh * wk.nt + cur_raw.tile) * SV_TY, cur_raw.x.b); // box {4 h, 128 t, 16 s}; rows past the end read as zeros
 		advance(cur_raw);
 	};
 	auto issue_kb = [&]() {
@@ -200,8 +202,8 @@ dense_bwd_sv_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_const
 			return;
 		}
 		mbar_expect_tx(&bars.gt_full[st], SV_B_BYTES);
-		tma_load_4d(gts + st * SV_GTSTAGE + SV_GT_BYTES, &kmap, &bars.gt_full[st], cur_kb.x.w0, cur_kb.x.h0, cur_kb.tile * SV_TY,
-			    cur_kb.x.b); // box {32 w, 4 h, 16 s}
+		tma_load_4d(gts + st * SV_GTSTAGE + SV_GT_BYTES, &kmap, &bars.gt_full[st], cur_kb.x.w0, cur_kb.x.h0,
+			    (cur_kb.x.sh * wk.nt + cur_kb.tile) * SV_TY, cur_kb.x.b); // box {32 w, 4 h, 16 s}
 		advance(cur_kb);
 	};
 	// This warp's row (s = warp) of tile m: g [t][h] -> [h][t] and its sum over t; then the warp's arrival for tile m.
@@ -283,7 +285,7 @@ dense_bwd_sv_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_const
 		float a[SV_XR], acc[SV_XR], rsq = 0.f;
 		float *item_pp;
 		size_t qoff;          // offset of this thread's first (query row, head, column) element in q and in d_q
-		int item_ok, rows_ok; // column in range; query rows i < rows_ok are in range
+		int src_left, rows_ok; // source rows from the item's first one to the end (0: column out of range); query rows i < rows_ok are in range
 		{
 			const SvItem x = sv_decode(wk, item);
 			const int hh = x.h0 + h, ww = x.w0 + lane, t0 = x.tb * SV_TX + xg * SV_XR;
@@ -297,8 +299,9 @@ dense_bwd_sv_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_const
 				off = sv_opaque(off + row);
 				acc[i] = 0.f;
 			}
-			item_pp = part + ((size_t(x.tb) * bs + x.b) * n_tok) * row + size_t(hh) * width + ww;
-			item_ok = col_ok ? 1 : 0;
+			const int s_first = x.sh * wk.nt * SV_TY; // the item's range of source rows starts here
+			item_pp = part + ((size_t(x.tb) * bs + x.b) * n_tok + s_first) * row + size_t(hh) * width + ww;
+			src_left = col_ok ? n_tok - s_first : 0;
 		}
 		for (int tile = 0; tile < wk.nt; tile++, n++) {
 			const int st = int(n & 1u);
@@ -313,7 +316,7 @@ dense_bwd_sv_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_const
 				reduce_prev(n - 1u);
 			red_pp = item_pp;
 			red_s0 = tile * SV_TY;
-			red_rows = sv_opaque(item_ok) != 0 ? n_tok - red_s0 : 0;
+			red_rows = sv_opaque(src_left) - red_s0;
 			transpose_row(n + 1);
 		}
 		// d_q of this thread's column: out = scale * (2 acc - row sum); the row sum of query row i sits in lane i and
@@ -325,7 +328,8 @@ dense_bwd_sv_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_const
 			volatile float *rs = rowsum + warp * 32;
 			rs[lane] = rsq;
 			__syncwarp();
-			size_t off = qoff; // advanced through the no-op so that the 32 addresses are formed one after the other, not all up front
+			// advanced through the no-op so that the 32 addresses are formed one after the other, not all up front
+			size_t off = qoff + size_t(sv_decode(wk, item).sh) * dq_stride;
 #pragma unroll
 			for (int i = 0; i < SV_XR; i++) {
 				if (i < rows_ok)
@@ -342,10 +346,11 @@ dense_bwd_sv_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_const
 	}
 }
 
-// d_k = -scale * sum over the query-row blocks of their shares, in block order.  n4 = float4 count of d_k.
+// d_k = -scale * sum over the query-row blocks of their shares, in block order; and, when the source rows were
+// split over ns items, d_q = sum of the ns partial d_q (already scaled), in order.  n4 = float4 count of d_k (= of d_q).
 __global__ void __launch_bounds__(256)
-dense_bwd_sv_partsum_kernel(const float4 *__restrict__ part, float4 *__restrict__ d_k, const int *__restrict__ tie_hdr,
-			    size_t n4, int ntb, float scale)
+dense_bwd_sv_partsum_kernel(const float4 *__restrict__ part, float4 *__restrict__ d_k, const float4 *__restrict__ dq_part,
+			    float4 *__restrict__ d_q, const int *__restrict__ tie_hdr, size_t n4, int ntb, int ns, float scale)
 {
 	if (tie_hdr[1] != 0)
 		return;
@@ -359,19 +364,33 @@ dense_bwd_sv_partsum_kernel(const float4 *__restrict__ part, float4 *__restrict_
 			s.w += v.w;
 		}
 		d_k[i] = make_float4(-scale * s.x, -scale * s.y, -scale * s.z, -scale * s.w);
+		if (ns > 1) {
+			float4 t = dq_part[i];
+			for (int r = 1; r < ns; r++) {
+				const float4 v = dq_part[size_t(r) * n4 + i];
+				t.x += v.x;
+				t.y += v.y;
+				t.z += v.z;
+				t.w += v.w;
+			}
+			d_q[i] = t;
+		}
 	}
 }
 
 } // namespace
 
 // Returns L1ATTN_OK, a negative error, or 1 when this path does not apply (then nothing was launched).
-// tie_hdr: filled by dense_ties_launch() earlier on the same stream; part: bwd_scratch_layout().part bytes.
+// tie_hdr: filled by dense_ties_launch() earlier on the same stream; part, dq_part: the d_k shares and the partial
+// d_q of bwd_scratch_layout() (dq_part is used only when that layout splits the source rows: ns > 1).
 int dense_bwd_sv_launch(const void *d_attn, const void *q, const void *k, void *d_q, void *d_k, const int *tie_hdr,
-			void *part, int bs, int n_tok, int n_heads, int width, int dtype, cudaStream_t st)
+			void *part, void *dq_part, int ns, int bs, int n_tok, int n_heads, int width, int dtype, cudaStream_t st)
 {
 	if (dtype != L1ATTN_F32 || width % 4 != 0 || n_heads % 4 != 0)
 		return 1; // row pitches of k and of d_attn must be multiples of 16 bytes for the tensor maps
-	for (const void *p : {d_attn, q, k, (const void *)d_q, (const void *)d_k, (const void *)part})
+	if (ns < 1 || (ns > 1 && !dq_part))
+		return 1;
+	for (const void *p : {d_attn, q, k, (const void *)d_q, (const void *)d_k, (const void *)part, (const void *)dq_part})
 		if (!aligned(p, 16))
 			return 1;
 	const uint64_t kdims[4] = {uint64_t(width), uint64_t(n_heads), uint64_t(n_tok), uint64_t(bs)};
@@ -391,24 +410,27 @@ int dense_bwd_sv_launch(const void *d_attn, const void *q, const void *k, void *
 	wk.nws = (width + SV_WS - 1) / SV_WS;
 	wk.ntb = (n_tok + SV_TX - 1) / SV_TX;
 	wk.nhg = (n_heads + SV_HG - 1) / SV_HG;
-	const long long total = (long long)bs * wk.nhg * wk.ntb * wk.nws;
+	wk.ns = unsigned(ns);
+	const long long total = (long long)bs * wk.nhg * wk.ntb * wk.nws * ns;
 	if (total > 0x7fffffffLL)
 		return 1;
 	wk.total = unsigned(total);
-	wk.nt = (n_tok + SV_TY - 1) / SV_TY;
+	wk.nt = ((n_tok + SV_TY - 1) / SV_TY + ns - 1) / ns; // per item; the last range may reach past the end (zero-filled loads, no stores)
 	int dev = 0, sms = 0;
 	L1B_CUDA(cudaGetDevice(&dev));
 	L1B_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
 	const unsigned grid = wk.total < unsigned(sms) ? wk.total : unsigned(sms);
 	L1B_CUDA(cudaFuncSetAttribute(dense_bwd_sv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(SV_SMEM)));
 	const float scale = float(-1.0 / sqrt(double(width)));
-	dense_bwd_sv_kernel<<<grid, SV_THREADS, SV_SMEM, st>>>(kmap, gmap, (const float *)q, (float *)d_q, (float *)part, tie_hdr, bs,
-							       n_tok, n_heads, width, scale, wk, err);
-	L1B_LAUNCH_CHECK();
 	const size_t n4 = size_t(bs) * n_tok * n_heads * width / 4;
+	dense_bwd_sv_kernel<<<grid, SV_THREADS, SV_SMEM, st>>>(kmap, gmap, (const float *)q, ns > 1 ? (float *)dq_part : (float *)d_q,
+							       ns > 1 ? n4 * 4 : size_t(0), (float *)part, tie_hdr, bs, n_tok, n_heads,
+							       width, scale, wk, err);
+	L1B_LAUNCH_CHECK();
 	const size_t want = (n4 + 255) / 256;
 	const unsigned pgrid = unsigned(want < size_t(sms) * 16 ? want : size_t(sms) * 16);
-	dense_bwd_sv_partsum_kernel<<<pgrid, 256, 0, st>>>((const float4 *)part, (float4 *)d_k, tie_hdr, n4, int(wk.ntb), scale);
+	dense_bwd_sv_partsum_kernel<<<pgrid, 256, 0, st>>>((const float4 *)part, (float4 *)d_k, (const float4 *)dq_part, (float4 *)d_q,
+							   tie_hdr, n4, int(wk.ntb), ns, scale);
 	L1B_LAUNCH_CHECK();
 	return L1ATTN_OK;
 }

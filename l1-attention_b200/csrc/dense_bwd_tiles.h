@@ -40,12 +40,39 @@ inline BwdFlagLayout bwd_flag_layout(int bs, int n_tok, int n_heads, int width)
 constexpr int BWD_TIE_CAP = 4096; // listed ties per call; more set the overflow word and the flagged exact loops run
 constexpr int BWD_SV_TX = 128;    // query rows per work item of the single-visit kernel: d_k leaves it as ceil(n_tok / 128) shares
 
+// The single-visit kernel's work items are (batch, 4 heads, 32 columns, 128 query rows); each walks all source
+// rows, or -- when that many items would leave much of the last wave of SMs empty (long context, small batch) --
+// one of `ns` equal ranges of them, leaving `ns` partial d_q that the summing kernel adds.  The choice depends on the
+// shape alone (the SM count is taken as B200's 148) so that the scratch size can be stated without a device.
+constexpr int BWD_SV_SMS = 148;
+inline double bwd_wave_fill(double items, int sms)
+{
+	const double waves = double((long long)((items + sms - 1) / sms));
+	return waves > 0 ? items / (waves * sms) : 0.0;
+}
+inline int bwd_sv_splits(int bs, int n_tok, int n_heads, int width)
+{
+	const double items = double(bs) * ((n_heads + 3) / 4) * ((width + 31) / 32) * ((n_tok + BWD_SV_TX - 1) / BWD_SV_TX);
+	int best = 1;
+	double best_fill = bwd_wave_fill(items, BWD_SV_SMS);
+	for (int ns = 2; ns <= 4; ns *= 2) {
+		if ((n_tok + 15) / 16 < 32 * ns)
+			break; // keep at least 32 tiles of 16 source rows per item
+		const double f = bwd_wave_fill(items * ns, BWD_SV_SMS);
+		if (f > best_fill * 1.03) { // (a split costs one more read-modify of d_q: not for a percent)
+			best = ns;
+			best_fill = f;
+		}
+	}
+	return best;
+}
+
 // Caller-provided scratch of the dense backward, in this order (every part 256-byte aligned):
-//   tie flags | tie header {count, overflow} | tie list uint4[BWD_TIE_CAP] | shares of d_k
+//   tie flags | tie header {count, overflow} | tie list uint4[BWD_TIE_CAP] | shares of d_k | partial d_q (if split)
 // The flags and the header are adjacent so that one memset clears both.
 struct BwdScratchLayout {
-	size_t flags, hdr, ties, part, bytes; // offsets, total
-	int ntb;
+	size_t flags, hdr, ties, part, dqpart, bytes; // offsets, total
+	int ntb, ns;
 };
 inline BwdScratchLayout bwd_scratch_layout(int bs, int n_tok, int n_heads, int width)
 {
@@ -56,7 +83,10 @@ inline BwdScratchLayout bwd_scratch_layout(int bs, int n_tok, int n_heads, int w
 	l.ties = l.hdr + 256;
 	l.part = l.ties + size_t(BWD_TIE_CAP) * 16;
 	l.ntb = (n_tok + BWD_SV_TX - 1) / BWD_SV_TX;
-	l.bytes = l.part + pad(size_t(l.ntb) * bs * n_tok * n_heads * width * 4);
+	l.ns = bwd_sv_splits(bs, n_tok, n_heads, width);
+	const size_t n = size_t(bs) * n_tok * n_heads * width * 4;
+	l.dqpart = l.part + pad(size_t(l.ntb) * n);
+	l.bytes = l.dqpart + (l.ns > 1 ? pad(size_t(l.ns) * n) : 0);
 	return l;
 }
 } // namespace l1b

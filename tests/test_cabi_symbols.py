@@ -86,6 +86,9 @@ def test_size_queries():
     assert lib.l1attn_sparse_bwd_scratch_bytes(8, 4096, 8, 32, 1) == 8 * 4096 * 8 * 32 * 8
     # tie flags (x per 4 rows, y per 16 rows, per pass and group) | tie header | 4096 tie entries | 8 shares of d_k
     assert lib.l1attn_dense_bwd_scratch_bytes(16, 1024, 16, 64, 0) == 2 * 64 * (256 + 64) + 256 + 4096 * 16 + 8 * 16 * 1024 * 16 * 64 * 4
+    # long context, two batch items: 32 shares of d_k, and the source rows split in two -> two partial d_q
+    n3 = 2 * 4096 * 8 * 128 * 4
+    assert lib.l1attn_dense_bwd_scratch_bytes(2, 4096, 8, 128, 0) == 2 * 8 * (1024 + 256) + 256 + 4096 * 16 + 32 * n3 + 2 * n3
     assert lib.l1attn_dense_bwd_scratch_bytes(16, 1024, 16, 64, 1) == 16  # float64 needs none
     assert lib.l1attn_expand_coo_scratch_bytes(4096) == 0
     assert lib.l1attn_expand_coo_scratch_bytes(1 << 20) == (1 << 20) * 8

@@ -14,7 +14,8 @@ TOL = {np.float32: 1e-5, np.float64: 1e-12}
 
 SHAPES = [(1, 1, 1, 1), (1, 16, 8, 64), (2, 5, 3, 7), (1, 9, 2, 33), (2, 17, 5, 16), (1, 33, 9, 65),
           (3, 70, 12, 32), (1, 130, 16, 64), (2, 64, 1, 128), (1, 3, 16, 7), (2, 40, 8, 97), (1, 65, 24, 64),
-          (2, 150, 4, 64), (1, 140, 20, 48)]  # (head counts that take the forward's four-head work items)
+          (2, 150, 4, 64), (1, 140, 20, 48),   # (head counts that take the forward's four-head work items)
+          (1, 1040, 4, 32), (1, 2050, 4, 32)]  # (few work items, many tokens: the backward splits the source rows in 2 and 4)
 
 
 def _cabi():
