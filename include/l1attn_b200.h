@@ -105,7 +105,8 @@ int l1attn_dense_fwd(const void *q, const void *k, void *attn,
  * backward, plus one flag per tile for the case that the list overflows (zero-padded tokens, q == k:
  * flagged tiles then take an exact loop).  The rest of the buffer receives the shares of d_k that the
  * single-visit kernel leaves per block of 128 query rows: ceil(n_tok / 128) * sizeof(d_k) bytes, i.e.
- * about width / 128 times the size of d_attn.  With NULL every tile takes the exact loop and no scratch is
+ * about width / 128 times the size of d_attn (plus 2 or 4 times sizeof(d_q) for shapes whose work items
+ * split their source rows: long context with a small batch).  With NULL every tile takes the exact loop and no scratch is
  * needed (same results, about 2.7 times the time in fp32).  Contents need no initialisation and mean
  * nothing after the call; calls that share a scratch buffer must not overlap on the GPU.
  * Replaces l1attn_cuda_drv.backward (cuda/l1attn_cuda_drv.cpp:67-104) and
