@@ -101,31 +101,32 @@ def test_ties_exact(dtype):
     assert_close(dk, rk, 2e-7 if dtype == np.float32 else 1e-14, "dk ties")
 
 
+@pytest.mark.parametrize("shape", [(2, 200, 8, 64), (1, 1040, 4, 32)])  # (the second: work items split their source rows in two)
 @pytest.mark.parametrize("kind", ["sparse_ties", "padded", "q_is_k", "grid"])
-def test_fast_backward_tie_handling(kind):
+def test_fast_backward_tie_handling(kind, shape):
     """fp32 shapes that take the compare-form backward (16-byte rows): a handful of planted ties, many
     zero-padded tokens (more candidates than the detector lists), q == k, and values on a coarse grid
     (ties everywhere).  The result must match the oracle as if every term had used sign(0) = 0."""
     from oracle import oracle
     cabi = _cabi()
     rng = np.random.RandomState(21)
-    shape = (2, 200, 8, 64)
+    bs, n, nh, nw = shape
     q = rng.standard_normal(shape).astype(np.float32)
     k = rng.standard_normal(shape).astype(np.float32)
     if kind == "sparse_ties":
         for _ in range(7):
-            b, t, s, h, w = (rng.randint(n) for n in (2, 200, 200, 8, 64))
+            b, t, s, h, w = (rng.randint(m) for m in (bs, n, n, nh, nw))
             k[b, s, h, w] = q[b, t, h, w]
-        k[1, 5, 3, 7] = -0.0
-        q[1, 9, 3, 7] = 0.0  # +0 == -0 is a tie too
+        k[bs - 1, 5, 3, 7] = -0.0
+        q[bs - 1, 9, 3, 7] = 0.0  # +0 == -0 is a tie too
     elif kind == "padded":
-        q[:, 120:] = 0
-        k[:, 90:] = 0
+        q[:, n * 3 // 5:] = 0
+        k[:, n * 9 // 20:] = 0
     elif kind == "q_is_k":
         k = q.copy()
     else:
         q, k = np.round(q * 2) / 2, np.round(k * 2) / 2
-    g = rng.standard_normal((2, 200, 200, 8)).astype(np.float32)
+    g = rng.standard_normal((bs, n, n, nh)).astype(np.float32)
     dq, dk = (x.cpu().numpy() for x in cabi.dense_bwd(_dev(g), _dev(q), _dev(k)))
     rq, rk = oracle.dense_bwd(g.astype(np.float64), q.astype(np.float64), k.astype(np.float64))
     assert_close(dq, rq, 1e-5, "dq " + kind)
