@@ -43,7 +43,7 @@ def nvcc():
 
 def build_lib(force=False, verbose=False):
     srcs = [os.path.join(CSRC, s) for s in CU_SOURCES]
-    deps = srcs + glob.glob(os.path.join(CSRC, "*.cuh")) + glob.glob(os.path.join(INC, "*.h"))
+    deps = srcs + glob.glob(os.path.join(CSRC, "*.cuh")) + glob.glob(os.path.join(CSRC, "*.h")) + glob.glob(os.path.join(INC, "*.h"))
     if not force and not _newer(LIB, deps):
         return LIB
     objs = []

@@ -41,9 +41,10 @@ constexpr int BWD_TIE_CAP = 4096; // listed ties per call; more set the overflow
 constexpr int BWD_SV_TX = 128;    // query rows per work item of the single-visit kernel: d_k leaves it as ceil(n_tok / 128) shares
 
 // The single-visit kernel's work items are (batch, 4 heads, 32 columns, 128 query rows); each walks all source
-// rows, or -- when that many items would leave much of the last wave of SMs empty (long context, small batch) --
-// one of `ns` equal ranges of them, leaving `ns` partial d_q that the summing kernel adds.  The choice depends on the
-// shape alone (the SM count is taken as B200's 148) so that the scratch size can be stated without a device.
+// rows, or -- when that many items would leave much of the last wave of SMs empty (long context, small batch, a
+// shard of a multi-GPU run) -- one of `ns` equal ranges of them, leaving `ns` partial d_q that the summing kernel
+// adds.  The choice depends on the shape alone (the SM count is taken as B200's 148) so that the scratch size can
+// be stated without a device.  An item's fixed cost (its q rows in, its d_q rows out) is taken as 0.4 tiles.
 constexpr int BWD_SV_SMS = 148;
 inline double bwd_wave_fill(double items, int sms)
 {
@@ -53,15 +54,17 @@ inline double bwd_wave_fill(double items, int sms)
 inline int bwd_sv_splits(int bs, int n_tok, int n_heads, int width)
 {
 	const double items = double(bs) * ((n_heads + 3) / 4) * ((width + 31) / 32) * ((n_tok + BWD_SV_TX - 1) / BWD_SV_TX);
+	const int tiles = (n_tok + 15) / 16;
 	int best = 1;
-	double best_fill = bwd_wave_fill(items, BWD_SV_SMS);
-	for (int ns = 2; ns <= 4; ns *= 2) {
-		if ((n_tok + 15) / 16 < 32 * ns)
-			break; // keep at least 32 tiles of 16 source rows per item
-		const double f = bwd_wave_fill(items * ns, BWD_SV_SMS);
-		if (f > best_fill * 1.03) { // (a split costs one more read-modify of d_q: not for a percent)
+	double best_eff = bwd_wave_fill(items, BWD_SV_SMS) * tiles / (tiles + 0.4);
+	for (int ns = 2; ns <= 8; ns *= 2) {
+		const double tp = double((tiles + ns - 1) / ns);
+		if (tp < 8)
+			break;
+		const double eff = bwd_wave_fill(items * ns, BWD_SV_SMS) * tp / (tp + 0.4);
+		if (eff > best_eff * 1.02) { // (not for a percent or two: a split costs one more pass over d_q)
 			best = ns;
-			best_fill = f;
+			best_eff = eff;
 		}
 	}
 	return best;

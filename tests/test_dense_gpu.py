@@ -15,7 +15,7 @@ TOL = {np.float32: 1e-5, np.float64: 1e-12}
 SHAPES = [(1, 1, 1, 1), (1, 16, 8, 64), (2, 5, 3, 7), (1, 9, 2, 33), (2, 17, 5, 16), (1, 33, 9, 65),
           (3, 70, 12, 32), (1, 130, 16, 64), (2, 64, 1, 128), (1, 3, 16, 7), (2, 40, 8, 97), (1, 65, 24, 64),
           (2, 150, 4, 64), (1, 140, 20, 48),   # (head counts that take the forward's four-head work items)
-          (1, 1040, 4, 32), (1, 2050, 4, 32)]  # (few work items, many tokens: the backward splits the source rows in 2 and 4)
+          (1, 300, 4, 32), (1, 600, 4, 32), (1, 1040, 4, 32), (1, 2050, 4, 32)]  # (few work items: the backward splits the source rows in 2, 4, 8 and 8)
 
 
 def _cabi():
@@ -101,7 +101,7 @@ def test_ties_exact(dtype):
     assert_close(dk, rk, 2e-7 if dtype == np.float32 else 1e-14, "dk ties")
 
 
-@pytest.mark.parametrize("shape", [(2, 200, 8, 64), (1, 1040, 4, 32)])  # (the second: work items split their source rows in two)
+@pytest.mark.parametrize("shape", [(2, 200, 8, 64), (1, 1040, 4, 32)])  # (the second: work items split their source rows)
 @pytest.mark.parametrize("kind", ["sparse_ties", "padded", "q_is_k", "grid"])
 def test_fast_backward_tie_handling(kind, shape):
     """fp32 shapes that take the compare-form backward (16-byte rows): a handful of planted ties, many
