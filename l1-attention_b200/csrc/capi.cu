@@ -36,24 +36,26 @@ int check_dense(const void *const *ptrs, int nptr, int bs, int n_tok, int n_head
 	return L1ATTN_OK;
 }
 
-// Per-device state of the *_host entry points: a grow-only device arena, three copy/compute streams and a
-// small pinned block for values read back asynchronously.
+// Per-device state of the *_host entry points: a grow-only device arena, one stream per PCIe direction, three
+// compute streams and a small pinned block for values read back asynchronously.
+// Every batch item of every call is a chain copy in -> kernels -> copy out across those streams (events in
+// between): ALL copies in go through one stream and ALL copies out through another, each in the order of the
+// calls, so both directions of the link stay busy at once -- also across calls: the inputs of an independent
+// backward cross while the scores of the preceding forward leave (measured on this PCIe 5 x16 host: 54 GB/s in
+// alone, 50 GB/s out alone, 90 GB/s with both; with the copies on the items' own streams the directions took
+// turns and a [16,1024,16,64] forward + backward took 42 ms instead of 31 ms).
 // Every call takes fresh slices of the arena (bump allocation), so calls enqueued one after the other without
-// a synchronisation in between never share device buffers and can run concurrently; l1attn_host_sync() waits
-// for all of them and makes the whole arena available again.
-constexpr int NPIPE = 3;  // streams one call rotates its batch items over
-constexpr int NBANK = 1;  // banks of streams that consecutive calls would alternate between.  Two banks let an independent
-                          // backward's copies in run beside the preceding forward's copies out; measured on a B200 host
-                          // (PCIe 5 x16) that was slower than one bank (45.5 vs 42.0 ms per [16,1024,16,64] step: the
-                          // link moves ~60 GB/s in total whichever way the traffic is split), so one bank it is
+// a synchronisation in between never share device buffers; l1attn_host_sync() waits for all of them and makes
+// the whole arena available again.
+constexpr int NPIPE = 3; // compute streams one call rotates its batch items over
 constexpr int NSTAT = 64;
 struct Arena {
 	void *base = nullptr;
 	size_t cap = 0, used = 0;
-	cudaStream_t all[NPIPE * NBANK] = {};
-	cudaStream_t *st = all; // the bank of the current call
-	int bank = 0;
-	cudaEvent_t ev = nullptr;
+	cudaStream_t st[NPIPE] = {};          // kernels
+	cudaStream_t s_in = nullptr, s_out = nullptr; // host -> device, device -> host
+	std::vector<cudaEvent_t> evs;         // pool, handed out in order, all free again after a sync
+	size_t nev = 0;
 	int32_t *stat = nullptr; // pinned, NSTAT words
 	int nstat = 0;
 	bool ready = false;
@@ -73,10 +75,12 @@ Arena *arena_for_current(int *rc)
 		g_arena.resize(dev + 1);
 	Arena *a = &g_arena[dev];
 	if (!a->ready) {
-		for (int i = 0; i < NPIPE * NBANK && e == cudaSuccess; i++)
-			e = cudaStreamCreateWithFlags(&a->all[i], cudaStreamNonBlocking);
+		for (int i = 0; i < NPIPE && e == cudaSuccess; i++)
+			e = cudaStreamCreateWithFlags(&a->st[i], cudaStreamNonBlocking);
 		if (e == cudaSuccess)
-			e = cudaEventCreateWithFlags(&a->ev, cudaEventDisableTiming);
+			e = cudaStreamCreateWithFlags(&a->s_in, cudaStreamNonBlocking);
+		if (e == cudaSuccess)
+			e = cudaStreamCreateWithFlags(&a->s_out, cudaStreamNonBlocking);
 		if (e == cudaSuccess)
 			e = cudaHostAlloc(reinterpret_cast<void **>(&a->stat), NSTAT * sizeof(int32_t), cudaHostAllocDefault);
 		if (e != cudaSuccess) {
@@ -85,16 +89,32 @@ Arena *arena_for_current(int *rc)
 		}
 		a->ready = true;
 	}
-	a->st = a->all + a->bank * NPIPE; // (the vector may have moved the object since the last call)
 	return a;
+}
+
+// `to` will not start what is enqueued on it from here on before everything enqueued on `from` so far has finished
+int stream_after(Arena *a, cudaStream_t to, cudaStream_t from)
+{
+	if (a->nev == a->evs.size()) {
+		cudaEvent_t ev;
+		L1B_CUDA(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+		a->evs.push_back(ev);
+	}
+	cudaEvent_t ev = a->evs[a->nev++];
+	L1B_CUDA(cudaEventRecord(ev, from));
+	L1B_CUDA(cudaStreamWaitEvent(to, ev, 0));
+	return L1ATTN_OK;
 }
 
 // Waits for everything the *_host calls have enqueued on this device; returns the first deferred status
 // (an out-of-range coo row found by an index build) and makes the arena's memory available again.
 int arena_sync(Arena *a)
 {
-	for (int i = 0; i < NPIPE * NBANK; i++)
-		L1B_CUDA(cudaStreamSynchronize(a->all[i]));
+	L1B_CUDA(cudaStreamSynchronize(a->s_in));
+	for (int i = 0; i < NPIPE; i++)
+		L1B_CUDA(cudaStreamSynchronize(a->st[i]));
+	L1B_CUDA(cudaStreamSynchronize(a->s_out));
+	a->nev = 0;
 	int rc = L1ATTN_OK;
 	for (int i = 0; i < a->nstat; i++)
 		if (a->stat[i] != 0 && rc == L1ATTN_OK)
@@ -108,26 +128,36 @@ size_t pad256(size_t n) { return (n + 255) / 256 * 256; }
 
 // Makes `bytes` more bytes available.  When the arena has to grow, or has no room left for a deferred status
 // word, everything in flight is waited for first (earlier asynchronous calls then simply finish early);
-// *deferred receives their status.
+// *deferred receives their status.  It grows to what the calls enqueued since the last synchronisation need
+// TOGETHER, so that the same sequence of calls fits next time without a wait in the middle (a forward and a
+// backward enqueued back to back would otherwise take turns on the link instead of sharing it).
 int arena_reserve(Arena *a, size_t bytes, int *deferred)
 {
 	*deferred = L1ATTN_OK;
-	a->bank = (a->bank + 1) % NBANK;
-	a->st = a->all + a->bank * NPIPE;
-	if (a->used + bytes <= a->cap && a->nstat < NSTAT)
+	const size_t need = a->used + bytes;
+	if (need <= a->cap && a->nstat < NSTAT)
 		return L1ATTN_OK;
 	*deferred = arena_sync(a);
 	if (*deferred == L1ATTN_ERR_CUDA)
 		return *deferred;
-	if (bytes <= a->cap)
+	if (need <= a->cap)
 		return L1ATTN_OK;
 	if (a->base) {
 		L1B_CUDA(cudaFree(a->base));
 		a->base = nullptr;
 		a->cap = 0;
 	}
-	L1B_CUDA(cudaMalloc(&a->base, bytes));
-	a->cap = bytes;
+	cudaError_t e = cudaMalloc(&a->base, need);
+	if (e != cudaSuccess && need > bytes) { // not enough memory for the whole sequence: room for this call alone
+		(void)cudaGetLastError();
+		e = cudaMalloc(&a->base, bytes);
+		if (e == cudaSuccess)
+			a->cap = bytes;
+	} else if (e == cudaSuccess) {
+		a->cap = need;
+	}
+	if (e != cudaSuccess)
+		return cuda_fail(e);
 	return L1ATTN_OK;
 }
 
@@ -223,12 +253,19 @@ extern "C" int l1attn_dense_bwd(const void *d_attn, const void *q, const void *k
 
 // ---------------------------------------------------------------- host-buffer entry points
 //
-// One batch item at a time, the items dealt out over the three streams in rotation: while item b computes, item
-// b+1's inputs cross PCIe in one direction and item b-1's results in the other.  The *_async forms return once
-// everything is enqueued; the plain forms add l1attn_host_sync().
+// One batch item at a time: its inputs go in on the copy-in stream, its kernels run on one of the three compute
+// streams (in rotation) once they have arrived, its results leave on the copy-out stream once the kernels are done.
+// While item b computes, item b+1's inputs cross PCIe in one direction and item b-1's results in the other.
+// The *_async forms return once everything is enqueued; the plain forms add l1attn_host_sync().
 
 #define H2D(dst, src, n, st) L1B_CUDA(cudaMemcpyAsync(dst, src, n, cudaMemcpyHostToDevice, st))
 #define D2H(dst, src, n, st) L1B_CUDA(cudaMemcpyAsync(dst, src, n, cudaMemcpyDeviceToHost, st))
+#define L1B_TRY(call)                \
+	do {                         \
+		const int rc_ = (call); \
+		if (rc_)             \
+			return rc_;  \
+	} while (0)
 
 extern "C" int l1attn_host_sync(void)
 {
@@ -264,11 +301,13 @@ extern "C" int l1attn_dense_fwd_host_async(const void *q, const void *k, void *a
 	for (int b = 0; b < bs; b++) {
 		cudaStream_t st = ar->st[b % NPIPE];
 		void *dq = arena_take(ar, nqk), *dk = arena_take(ar, nqk), *da = arena_take(ar, na);
-		H2D(dq, off(q, b * nqk), nqk, st);
-		H2D(dk, off(k, b * nqk), nqk, st);
+		H2D(dq, off(q, b * nqk), nqk, ar->s_in);
+		H2D(dk, off(k, b * nqk), nqk, ar->s_in);
+		L1B_TRY(stream_after(ar, st, ar->s_in));
 		if ((rc = dense_fwd_launch(dq, dk, da, 1, n_tok, n_heads, width, dtype, st)))
 			return rc;
-		D2H(off(attn, b * na), da, na, st);
+		L1B_TRY(stream_after(ar, ar->s_out, st));
+		D2H(off(attn, b * na), da, na, ar->s_out);
 	}
 	return deferred;
 }
@@ -304,12 +343,14 @@ extern "C" int l1attn_dense_softmax_v_fwd_host(const void *q, const void *k, con
 		for (int b = 0; b < bs; b++) {
 			cudaStream_t st = ar->st[b % NPIPE];
 			void *dq = arena_take(ar, nqk), *dk = arena_take(ar, nqk), *dv = arena_take(ar, nv), *dvo = arena_take(ar, nv);
-			H2D(dq, off(q, b * nqk), nqk, st);
-			H2D(dk, off(k, b * nqk), nqk, st);
-			H2D(dv, off(v, b * nv), nv, st);
+			H2D(dq, off(q, b * nqk), nqk, ar->s_in);
+			H2D(dk, off(k, b * nqk), nqk, ar->s_in);
+			H2D(dv, off(v, b * nv), nv, ar->s_in);
+			L1B_TRY(stream_after(ar, st, ar->s_in));
 			if ((rc = dense_softmax_v_launch(dq, dk, dv, dvo, nullptr, 1, n_tok, n_heads, width, v_width, mode, dtype, st)))
 				return rc;
-			D2H(off(vo, b * nv), dvo, nv, st);
+			L1B_TRY(stream_after(ar, ar->s_out, st));
+			D2H(off(vo, b * nv), dvo, nv, ar->s_out);
 		}
 	}
 	return first_error(deferred, l1attn_host_sync());
@@ -338,13 +379,15 @@ extern "C" int l1attn_dense_bwd_host_async(const void *d_attn, const void *q, co
 		cudaStream_t st = ar->st[b % NPIPE];
 		void *dq = arena_take(ar, nqk), *dk = arena_take(ar, nqk), *dg = arena_take(ar, na);
 		void *ddq = arena_take(ar, nqk), *ddk = arena_take(ar, nqk), *dsc = arena_take(ar, nsc);
-		H2D(dq, off(q, b * nqk), nqk, st);
-		H2D(dk, off(k, b * nqk), nqk, st);
-		H2D(dg, off(d_attn, b * na), na, st);
+		H2D(dq, off(q, b * nqk), nqk, ar->s_in);
+		H2D(dk, off(k, b * nqk), nqk, ar->s_in);
+		H2D(dg, off(d_attn, b * na), na, ar->s_in);
+		L1B_TRY(stream_after(ar, st, ar->s_in));
 		if ((rc = dense_bwd_launch(dg, dq, dk, ddq, ddk, dsc, 1, n_tok, n_heads, width, dtype, st)))
 			return rc;
-		D2H(off(d_q, b * nqk), ddq, nqk, st);
-		D2H(off(d_k, b * nqk), ddk, nqk, st);
+		L1B_TRY(stream_after(ar, ar->s_out, st));
+		D2H(off(d_q, b * nqk), ddq, nqk, ar->s_out);
+		D2H(off(d_k, b * nqk), ddk, nqk, ar->s_out);
 	}
 	return deferred;
 }
@@ -356,8 +399,9 @@ extern "C" int l1attn_dense_bwd_host(const void *d_attn, const void *q, const vo
 	return first_error(rc, l1attn_host_sync());
 }
 
-// coo -> device, edge index built on the first stream; the other streams wait for it.  The status word of the
-// index build (an out-of-range row) is read back into the pinned block and reported by the next l1attn_host_sync().
+// coo -> device, edge index built on the first compute stream; the other compute streams wait for it.  The status
+// word of the index build (an out-of-range row) is read back into the pinned block and reported by the next
+// l1attn_host_sync().
 static int host_index(Arena *ar, const int32_t *coo, int cl, int n_tok, int dst_mxlen, void **dix)
 {
 	const size_t nc = size_t(cl) * 16, nix = l1attn_sparse_index_bytes(cl, n_tok, dst_mxlen);
@@ -365,16 +409,17 @@ static int host_index(Arena *ar, const int32_t *coo, int cl, int n_tok, int dst_
 	*dix = arena_take(ar, nix);
 	int32_t *dstat = static_cast<int32_t *>(arena_take(ar, 4));
 	if (cl)
-		H2D(dc, coo, nc, ar->st[0]);
+		H2D(dc, coo, nc, ar->s_in);
+	L1B_TRY(stream_after(ar, ar->st[0], ar->s_in));
 	int rc = l1attn_sparse_build_index(static_cast<int32_t *>(dc), cl, n_tok, dst_mxlen, *dix, dstat, ar->st[0]);
 	if (rc)
 		return rc;
 	int32_t *hstat = &ar->stat[ar->nstat++];
 	*hstat = 0;
-	D2H(hstat, dstat, 4, ar->st[0]);
-	L1B_CUDA(cudaEventRecord(ar->ev, ar->st[0]));
+	L1B_TRY(stream_after(ar, ar->s_out, ar->st[0]));
+	D2H(hstat, dstat, 4, ar->s_out);
 	for (int i = 1; i < NPIPE; i++)
-		L1B_CUDA(cudaStreamWaitEvent(ar->st[i], ar->ev, 0));
+		L1B_TRY(stream_after(ar, ar->st[i], ar->st[0]));
 	return L1ATTN_OK;
 }
 
@@ -409,17 +454,19 @@ extern "C" int l1attn_sparse_fwd_host_async(const void *v, const void *vb, const
 		cudaStream_t st = ar->st[b % NPIPE];
 		void *dv = arena_take(ar, nv), *dvb = arena_take(ar, nv), *dq = arena_take(ar, nqk), *dk = arena_take(ar, nqk);
 		void *dvo = arena_take(ar, nv), *da = arena_take(ar, na);
-		H2D(dv, off(v, b * nv), nv, st);
+		H2D(dv, off(v, b * nv), nv, ar->s_in);
 		if (bidi)
-			H2D(dvb, off(vb, b * nv), nv, st);
-		H2D(dq, off(q, b * nqk), nqk, st);
-		H2D(dk, off(k, b * nqk), nqk, st);
+			H2D(dvb, off(vb, b * nv), nv, ar->s_in);
+		H2D(dq, off(q, b * nqk), nqk, ar->s_in);
+		H2D(dk, off(k, b * nqk), nqk, ar->s_in);
+		L1B_TRY(stream_after(ar, st, ar->s_in));
 		if ((rc = l1attn_sparse_fwd(dv, dvb, dq, dk, dix, dvo, da, 1, n_tok, n_heads, width, v_width, cl, dst_mxlen,
 					    use_softmax, bidi, dtype, st)))
 			return rc;
-		D2H(off(vo, b * nv), dvo, nv, st);
+		L1B_TRY(stream_after(ar, ar->s_out, st));
+		D2H(off(vo, b * nv), dvo, nv, ar->s_out);
 		if (na)
-			D2H(off(attn, b * na), da, na, st);
+			D2H(off(attn, b * na), da, na, ar->s_out);
 	}
 	return deferred;
 }
@@ -467,22 +514,24 @@ extern "C" int l1attn_sparse_bwd_host_async(const void *dvo, const void *v, cons
 		void *dq = arena_take(ar, nqk), *dk = arena_take(ar, nqk), *da = arena_take(ar, na);
 		void *gdv = arena_take(ar, nv), *gdvb = arena_take(ar, nv), *gdq = arena_take(ar, nqk), *gdk = arena_take(ar, nqk);
 		void *dx = arena_take(ar, na);
-		H2D(ddvo, off(dvo, b * nv), nv, st);
-		H2D(dv, off(v, b * nv), nv, st);
+		H2D(ddvo, off(dvo, b * nv), nv, ar->s_in);
+		H2D(dv, off(v, b * nv), nv, ar->s_in);
 		if (bidi)
-			H2D(dvb, off(vb, b * nv), nv, st);
-		H2D(dq, off(q, b * nqk), nqk, st);
-		H2D(dk, off(k, b * nqk), nqk, st);
+			H2D(dvb, off(vb, b * nv), nv, ar->s_in);
+		H2D(dq, off(q, b * nqk), nqk, ar->s_in);
+		H2D(dk, off(k, b * nqk), nqk, ar->s_in);
 		if (na)
-			H2D(da, off(attn, b * na), na, st);
+			H2D(da, off(attn, b * na), na, ar->s_in);
+		L1B_TRY(stream_after(ar, st, ar->s_in));
 		if ((rc = l1attn_sparse_bwd(ddvo, dv, dvb, dq, dk, dix, da, gdv, gdvb, gdq, gdk, dx, 1, n_tok, n_heads, width,
 					    v_width, cl, dst_mxlen, use_softmax, bidi, dtype, st)))
 			return rc;
-		D2H(off(d_v, b * nv), gdv, nv, st);
+		L1B_TRY(stream_after(ar, ar->s_out, st));
+		D2H(off(d_v, b * nv), gdv, nv, ar->s_out);
 		if (bidi)
-			D2H(off(d_vb, b * nv), gdvb, nv, st);
-		D2H(off(d_q, b * nqk), gdq, nqk, st);
-		D2H(off(d_k, b * nqk), gdk, nqk, st);
+			D2H(off(d_vb, b * nv), gdvb, nv, ar->s_out);
+		D2H(off(d_q, b * nqk), gdq, nqk, ar->s_out);
+		D2H(off(d_k, b * nqk), gdk, nqk, ar->s_out);
 	}
 	return deferred;
 }
