@@ -1,5 +1,6 @@
 """Run under torch.distributed.run with one rank per GPU (launched by test_modules_gpu.py when the box has the GPUs):
-the dense operator over DenseGridShard's square blocks against the single-GPU operator on the whole problem.
+the dense operator over DenseGridShard's square blocks, and the sparse operator over SparseShard's head groups and
+dst-token ranges, against the single-GPU operators on the whole problem.
 Rank 0 prints "grid-ok" when every rank agrees."""
 import os
 import sys
@@ -39,6 +40,29 @@ def main():
                 rel(dk, rdk[m["b0"]:m["b1"], m["s0"]:m["s1"], m["h0"]:m["h1"]]))
         if not (errs[0] == 0.0 and errs[1] < 1e-5 and errs[2] < 1e-5):  # scores: same kernel, same operands; sums: other order
             print("rank %d shape %s: %s  %s" % (rank, shape, errs, plan.describe()), flush=True)
+            bad += 1
+    # the sparse operator by (batch item, head group) and by dst-token range (one all-reduce of d_k, d_v) against
+    # the single-GPU operator on the whole problem
+    bs, n, h, w = 1, 300, 8, 32
+    gen = torch.Generator().manual_seed(13)
+    co = torch.stack([torch.randint(0, n, (2500,), generator=gen), torch.randint(0, n, (2500,), generator=gen)], 1)
+    geng = torch.Generator(device=dev).manual_seed(17)
+    q, k = (0.5 * torch.randn((bs, n, h, w), generator=geng, device=dev) for _ in range(2))
+    v, dvo = (torch.randn((bs, n, h, w), generator=geng, device=dev) for _ in range(2))
+    whole = sh.SparseShard(co, bs, n, 0, 1, device=dev, n_heads=h)
+    ref = [x.clone() for x in whole.forward_backward(v, q, k, dvo, True)]
+    rel = lambda a, b: float((a - b).norm() / b.norm().clamp_min(1e-30))
+    for mode in ("head", "dst"):
+        plan = sh.SparseShard(co, bs, n, rank, world, device=dev, n_heads=h, mode=mode)
+        got = plan.forward_backward(v, q, k, dvo, True)
+        if mode == "head":
+            sl = (slice(plan.b0, plan.b1), slice(None), slice(plan.h0, plan.h1))
+            errs = [rel(g, r[sl]) for g, r in zip(got, ref)]
+        else:
+            rows = (slice(None), slice(plan.d0, plan.d1))
+            errs = [rel(got[0][rows], ref[0][rows]), rel(got[1], ref[1]), rel(got[2][rows], ref[2][rows]), rel(got[3], ref[3])]
+        if not all(e < 1e-5 for e in errs):
+            print("rank %d sparse %s: %s  %s" % (rank, mode, errs, plan.describe()), flush=True)
             bad += 1
     t = torch.tensor([bad], device=dev)
     dist.all_reduce(t)
