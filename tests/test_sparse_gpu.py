@@ -244,6 +244,22 @@ def test_host_buffer_entry_points():
             assert_close(x, r, 1e-5)
 
 
+def test_host_entry_point_reports_out_of_range_rows():
+    """The index build's verdict comes back through the copy-out stream and is reported by the synchronisation."""
+    cabi = _cabi()
+    rng = np.random.RandomState(6)
+    bs, n, h, w = 2, 12, 4, 16
+    q, k, v = (rng.standard_normal((bs, n, h, w)).astype(np.float32) for _ in range(3))
+    coo = np.array([[0, 1, 0, 0], [40, 1, 0, 0], [1, 1, 0, 1]], dtype=np.int32)  # dst 40 of 12 tokens
+    with pytest.raises(cabi.L1AttnError) as e:
+        cabi.sparse_fwd_host(v, q, k, coo, 2, True)
+    assert e.value.code == -4
+    # and the library is usable afterwards
+    good = np.array([[0, 1, 0, 0], [1, 1, 0, 1]], dtype=np.int32)
+    vo, attn = cabi.sparse_fwd_host(v, q, k, good, 1, True)
+    assert np.isfinite(vo).all()
+
+
 def test_deterministic():
     rng = np.random.RandomState(8)
     from oracle import oracle
