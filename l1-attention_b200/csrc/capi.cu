@@ -43,7 +43,7 @@ int check_dense(const void *const *ptrs, int nptr, int bs, int n_tok, int n_head
 // calls, so both directions of the link stay busy at once -- also across calls: the inputs of an independent
 // backward cross while the scores of the preceding forward leave (measured on this PCIe 5 x16 host: 54 GB/s in
 // alone, 50 GB/s out alone, 90 GB/s with both; with the copies on the items' own streams the directions took
-// turns and a [16,1024,16,64] forward + backward took 42 ms instead of 31 ms).
+// turns and a [16,1024,16,64] forward + backward took 42 ms instead of 29 ms).
 // Every call takes fresh slices of the arena (bump allocation), so calls enqueued one after the other without
 // a synchronisation in between never share device buffers; l1attn_host_sync() waits for all of them and makes
 // the whole arena available again.
@@ -277,6 +277,16 @@ extern "C" int l1attn_host_sync(void)
 	return arena_sync(ar);
 }
 
+// Batch items per chain of the dense host entry points: copies of ~128 MB use the link better than smaller ones, but
+// a call should still be at least eight chains long so that the pipeline fills.
+static int host_group(int bs, size_t bytes_per_item)
+{
+	int g = 1;
+	while (g < 8 && size_t(2 * g) * bytes_per_item <= (size_t(160) << 20) && bs / (2 * g) >= 8)
+		g *= 2;
+	return g;
+}
+
 // keeps the first error of an asynchronous call and of the deferred statuses it had to collect on the way
 static int first_error(int a, int b) { return a != L1ATTN_OK ? a : b; }
 
@@ -298,16 +308,18 @@ extern "C" int l1attn_dense_fwd_host_async(const void *q, const void *k, void *a
 	int deferred;
 	if ((rc = arena_reserve(ar, size_t(bs) * (2 * pad256(nqk) + pad256(na)), &deferred)))
 		return rc;
-	for (int b = 0; b < bs; b++) {
-		cudaStream_t st = ar->st[b % NPIPE];
-		void *dq = arena_take(ar, nqk), *dk = arena_take(ar, nqk), *da = arena_take(ar, na);
-		H2D(dq, off(q, b * nqk), nqk, ar->s_in);
-		H2D(dk, off(k, b * nqk), nqk, ar->s_in);
+	const int G = host_group(bs, na);
+	for (int b = 0, it = 0; b < bs; b += G, it++) {
+		const int g = bs - b < G ? bs - b : G; // batch items of this chain
+		cudaStream_t st = ar->st[it % NPIPE];
+		void *dq = arena_take(ar, g * nqk), *dk = arena_take(ar, g * nqk), *da = arena_take(ar, g * na);
+		H2D(dq, off(q, b * nqk), g * nqk, ar->s_in);
+		H2D(dk, off(k, b * nqk), g * nqk, ar->s_in);
 		L1B_TRY(stream_after(ar, st, ar->s_in));
-		if ((rc = dense_fwd_launch(dq, dk, da, 1, n_tok, n_heads, width, dtype, st)))
+		if ((rc = dense_fwd_launch(dq, dk, da, g, n_tok, n_heads, width, dtype, st)))
 			return rc;
 		L1B_TRY(stream_after(ar, ar->s_out, st));
-		D2H(off(attn, b * na), da, na, ar->s_out);
+		D2H(off(attn, b * na), da, g * na, ar->s_out);
 	}
 	return deferred;
 }
@@ -371,23 +383,25 @@ extern "C" int l1attn_dense_bwd_host_async(const void *d_attn, const void *q, co
 	Arena *ar = arena_for_current(&rc);
 	if (!ar)
 		return rc;
-	const size_t nsc = dense_bwd_scratch_bytes(1, n_tok, n_heads, width, dtype);
+	const int G = host_group(bs, na);
+	const size_t nsc = dense_bwd_scratch_bytes(G, n_tok, n_heads, width, dtype);
 	int deferred;
-	if ((rc = arena_reserve(ar, size_t(bs) * (4 * pad256(nqk) + pad256(na) + pad256(nsc)), &deferred)))
+	if ((rc = arena_reserve(ar, size_t(bs) * (4 * pad256(nqk) + pad256(na)) + size_t((bs + G - 1) / G) * pad256(nsc) + 4096, &deferred)))
 		return rc;
-	for (int b = 0; b < bs; b++) {
-		cudaStream_t st = ar->st[b % NPIPE];
-		void *dq = arena_take(ar, nqk), *dk = arena_take(ar, nqk), *dg = arena_take(ar, na);
-		void *ddq = arena_take(ar, nqk), *ddk = arena_take(ar, nqk), *dsc = arena_take(ar, nsc);
-		H2D(dq, off(q, b * nqk), nqk, ar->s_in);
-		H2D(dk, off(k, b * nqk), nqk, ar->s_in);
-		H2D(dg, off(d_attn, b * na), na, ar->s_in);
+	for (int b = 0, it = 0; b < bs; b += G, it++) {
+		const int g = bs - b < G ? bs - b : G;
+		cudaStream_t st = ar->st[it % NPIPE];
+		void *dq = arena_take(ar, g * nqk), *dk = arena_take(ar, g * nqk), *dg = arena_take(ar, g * na);
+		void *ddq = arena_take(ar, g * nqk), *ddk = arena_take(ar, g * nqk), *dsc = arena_take(ar, nsc);
+		H2D(dq, off(q, b * nqk), g * nqk, ar->s_in);
+		H2D(dk, off(k, b * nqk), g * nqk, ar->s_in);
+		H2D(dg, off(d_attn, b * na), g * na, ar->s_in);
 		L1B_TRY(stream_after(ar, st, ar->s_in));
-		if ((rc = dense_bwd_launch(dg, dq, dk, ddq, ddk, dsc, 1, n_tok, n_heads, width, dtype, st)))
+		if ((rc = dense_bwd_launch(dg, dq, dk, ddq, ddk, dsc, g, n_tok, n_heads, width, dtype, st)))
 			return rc;
 		L1B_TRY(stream_after(ar, ar->s_out, st));
-		D2H(off(d_q, b * nqk), ddq, nqk, ar->s_out);
-		D2H(off(d_k, b * nqk), ddk, nqk, ar->s_out);
+		D2H(off(d_q, b * nqk), ddq, g * nqk, ar->s_out);
+		D2H(off(d_k, b * nqk), ddk, g * nqk, ar->s_out);
 	}
 	return deferred;
 }
