@@ -2,6 +2,7 @@
 // entry points (copy in, run, copy out) with their per-device arena.
 #include <cstdint>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <vector>
@@ -281,6 +282,8 @@ extern "C" int l1attn_host_sync(void)
 // a call should still be at least eight chains long so that the pipeline fills.
 static int host_group(int bs, size_t bytes_per_item)
 {
+	if (const char *e = getenv("L1ATTN_HOST_GROUP")) // experiments: fixed group size
+		return atoi(e) > 0 ? atoi(e) : 1;
 	int g = 1;
 	while (g < 8 && size_t(2 * g) * bytes_per_item <= (size_t(160) << 20) && bs / (2 * g) >= 8)
 		g *= 2;
