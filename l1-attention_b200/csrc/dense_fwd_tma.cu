@@ -284,9 +284,11 @@ int dense_fwd_tma_launch(const void *q, const void *k, void *attn, int bs, int n
 		return 1;
 	if (dtype != L1ATTN_F32)
 		return 1; // an 8 x 8 tile of doubles does not fit the register file; fp64 uses the generic kernel
-	// groups of four heads where they leave fewer lanes idle than groups of eight (4, 12, 20 ... heads)
-	const int idle8 = (n_heads + 7) / 8 * 8 - n_heads, idle4 = (n_heads + 3) / 4 * 4 - n_heads;
-	if (idle4 < idle8)
+	// groups of four heads (x 128 query rows) where they leave fewer lanes idle than groups of eight (x 64 query rows):
+	// 4, 12, 20 ... heads, unless the token count pads badly to 128
+	const long long work8 = (long long)((n_heads + 7) / 8 * 8) * ((n_tok + 63) / 64 * 64);
+	const long long work4 = (long long)((n_heads + 3) / 4 * 4) * ((n_tok + 127) / 128 * 128);
+	if (work4 < work8)
 		return launch<float, 4>((const float *)q, (const float *)k, (float *)attn, bs, n_tok, n_heads, width, st);
 	return launch<float, 8>((const float *)q, (const float *)k, (float *)attn, bs, n_tok, n_heads, width, st);
 }
