@@ -176,6 +176,9 @@ def _cuda_dense_ops():
     return Ops()
 
 
+_GROUPS = {}  # process groups by rank tuple: created once per process, whatever number of plans is built
+
+
 class DenseGridShard:
     """L1Attn forward + backward of ONE global problem [bs, n_tok, n_heads, width] over `world` ranks.
 
@@ -184,7 +187,7 @@ class DenseGridShard:
     query rows but only the keys of its block, and its d_k its key rows but only its queries: ONE all-reduce of
     d_q over the ranks of the same query block and ONE of d_k over those of the same key block complete them
     (none when a rank holds whole batch items).  All ranks must construct this object at the same point: it
-    creates the process groups.  No kernel reads another GPU's memory; the sums go through torch.distributed.
+    creates the process groups it needs (once per process and set of ranks).  No kernel reads another GPU's memory; the sums go through torch.distributed.
 
     `ops` is the compute backend (default: this library; the CPU tests of the partition logic pass a stand-in)."""
 
@@ -195,14 +198,13 @@ class DenseGridShard:
         self.ops = ops if ops is not None else _cuda_dense_ops()
         self.row_group = self.col_group = None
         # every rank creates every group, in the same order (new_group is collective over the whole job)
-        seen = {}
         if world > 1 and dist.is_available() and dist.is_initialized():
             for p in self.part:
                 for key in (tuple(p["row"]), tuple(p["col"])):
-                    if len(key) > 1 and key not in seen:
-                        seen[key] = dist.new_group(list(key))
-            self.row_group = seen.get(tuple(self.me["row"]))
-            self.col_group = seen.get(tuple(self.me["col"]))
+                    if len(key) > 1 and key not in _GROUPS:
+                        _GROUPS[key] = dist.new_group(list(key))
+            self.row_group = _GROUPS.get(tuple(self.me["row"]))
+            self.col_group = _GROUPS.get(tuple(self.me["col"]))
         self._scratch = None
 
     def local_inputs(self, q, k):
